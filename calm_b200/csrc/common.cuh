@@ -57,7 +57,7 @@ __device__ __forceinline__ void pdl_launch_next() {
 __device__ __forceinline__ void pdl_wait_prev() {
 	asm volatile("griddepcontrol.wait;" ::: "memory");
 }
-// L2 prefetch of a contiguous range (<= 16 KB, multiple of 16), issued by one thread; fire-and-forget (SASS UBLKPF)
+// L2 prefetch of a contiguous range (<= 16 KB, multiple of 16), issued by one thread; fire-and-forget
 __device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
 	asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
@@ -95,7 +95,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
 	while (!mbar_try_wait(bar, parity)) {
 	}
 }
-// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; completion is counted on `bar` (SASS UBLKCP)
+// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; completion is counted on `bar`
 __device__ __forceinline__ void tma_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
 	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes),
 	             "r"(smem_u32(bar))
