@@ -1,0 +1,513 @@
+// seqkernels.cuh -- device code of the layer-list models (include/calm_b200_seq.h): packed batches of tokens from many
+// sequences, a paged cache for what is indexed by position and per-slot buffers for what is recurrent.
+//
+// Precision: the residual stream, every norm, softmax, the convolution state, the recurrent state and everything that
+// feeds the recurrence after the projections are fp32.  Products read activations of type AT: float (exact mode, SIMT
+// FMA) or bf16 (tensor cores, fp32 accumulation).  Weights are bf16 as stored.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+// per-step description of the packed batch (device arrays)
+struct SeqBatch {
+	const int* tok;      // [N] token ids
+	const int* tslot;    // [N] slot of the token's sequence
+	const int* tpos;     // [N] position of the token in its sequence
+	const int* tfirst;   // [N] packed index of the first token its sequence has in this step
+	const int* sstart;   // [B] first packed index of sequence b
+	const int* scount;   // [B]
+	const int* spos0;    // [B] position of its first new token
+	const int* sslot;    // [B]
+	const int* pages;    // [slots][max_pages] page table
+	int N, B, max_pages, page;
+};
+
+__device__ __forceinline__ long cache_row(const SeqBatch& sb, int slot, int pos) {
+	return (long)sb.pages[(long)slot * sb.max_pages + pos / sb.page] * sb.page + pos % sb.page;
+}
+
+template <typename T>
+__device__ __forceinline__ T to_act(float v);
+template <>
+__device__ __forceinline__ float to_act<float>(float v) {
+	return v;
+}
+template <>
+__device__ __forceinline__ bf16 to_act<bf16>(float v) {
+	return __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// warp_sum / warp_max: common.cuh
+
+// ---------------------------------------------------------------- embedding, norms, small element-wise kernels
+
+// x[n] = E[tok[n]] (and a second copy when a looped span re-adds the embedding)
+__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width) {
+	const int n = blockIdx.x;
+	const bf16* e = table + (size_t)tok[n] * width;
+	for (int i = threadIdx.x; i < width; i += blockDim.x) {
+		const float v = ldf(e + i);
+		x[(size_t)n * width + i] = v;
+		if (x0) x0[(size_t)n * width + i] = v;
+	}
+}
+
+__global__ void k_seq_add(float* x, const float* y, size_t n) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i < n) x[i] += y[i];
+}
+
+// Dynamic Tanh: out[r][i] = tanh(alpha * x[rows ? rows[r] : r][i]) * w[i] + b[i]
+template <typename AT>
+__global__ void k_seq_dyt(AT* out, const float* x, const int* rows, const bf16* w, const bf16* b, const bf16* alpha, int R, int width) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)R * width) return;
+	const int r = (int)(i / width), c = (int)(i % width);
+	const float a = ldf(alpha);
+	const size_t src = (size_t)(rows ? rows[r] : r) * width + c;
+	out[i] = to_act<AT>(tanhf(a * x[src]) * ldf(w + c) + ldf(b + c));
+}
+
+// RMS norm with a weight over `len` columns of src rows: segment s of blockIdx.y.  Segment 0 goes to an activation
+// matrix, segment 1 (the cached latent) to its cache row.
+struct RmsSeg {
+	int col, len;
+	const bf16* w;
+};
+template <typename AT>
+__global__ void k_seq_latent_norm(const float* proj, int ldp, RmsSeg sq, RmsSeg sc, AT* cq, float* cache, SeqBatch sb, float eps) {
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+	if (n >= sb.N) return;
+	const RmsSeg s = blockIdx.y ? sc : sq;
+	const float* src = proj + (size_t)n * ldp + s.col;
+	float ss = 0.f;
+	for (int i = lane; i < s.len; i += 32) ss += src[i] * src[i];
+	ss = warp_sum(ss);
+	const float r = 1.f / sqrtf(ss / (float)s.len + eps);
+	if (blockIdx.y == 0) {
+		AT* d = cq + (size_t)n * s.len;
+		for (int i = lane; i < s.len; i += 32) d[i] = to_act<AT>(src[i] * r * ldf(s.w + i));
+	} else {
+		float* d = cache + cache_row(sb, sb.tslot[n], sb.tpos[n]) * s.len;
+		for (int i = lane; i < s.len; i += 32) d[i] = src[i] * r * ldf(s.w + i);
+	}
+}
+
+// copy `len` columns of fp32 rows into an activation matrix
+template <typename AT>
+__global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int len, int N) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)N * len) return;
+	out[i] = to_act<AT>(src[(i / len) * lds + col + i % len]);
+}
+
+// feed-forward unit on the stacked [gate | up] product: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1)
+template <typename AT>
+__global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)N * ff) return;
+	const size_t n = i / ff, c = i % ff;
+	const float g = fminf(gu[n * 2 * ff + c], limit);
+	const float u = fminf(fmaxf(gu[n * 2 * ff + ff + c], -limit), limit);
+	out[i] = to_act<AT>(g * sigmoidf_(1.702f * g) * (u + 1.f));
+}
+
+// ---------------------------------------------------------------- short convolution + activation + per-head norm (+ cache append)
+
+// One of q / k / v: `heads` vectors of `hd` channels starting at column `col` of the projection.
+struct ConvSeg {
+	int col, heads, hd;
+	int act;     // 1: SiLU after the convolution
+	int norm;    // 0 none, 1 unit vector (sum of squares + 1e-6), 2 RMS (mean of squares + eps)
+	float mul;   // factor after the norm
+	int to_cache;
+	float* dst;  // [N][heads*hd], or the cache [rows][heads*hd]
+};
+struct ConvArgs {
+	ConvSeg seg[3];
+	const float* proj;
+	int ldp;
+	const bf16* w;      // [channels][taps]
+	int taps, channels; // channels = all of q|k|v
+	const float* state; // [slots][taps-1][channels]: the projected values of the taps-1 positions before the step
+	float eps;
+};
+// one warp per (token, head vector)
+__global__ void k_seq_conv_heads(ConvArgs a, SeqBatch sb) {
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int n = blockIdx.x;
+	int u = blockIdx.y * (blockDim.x >> 5) + warp, s = 0;
+	while (s < 3 && u >= a.seg[s].heads) u -= a.seg[s].heads, ++s;
+	if (s == 3) return;
+	const ConvSeg sg = a.seg[s];
+	const int slot = sb.tslot[n], pos = sb.tpos[n];
+	const int back = n - sb.tfirst[n]; // tokens of this step before this one
+	const int T1 = a.taps - 1;
+	const float* st = a.state + (size_t)slot * T1 * a.channels;
+	float* d = sg.dst + (sg.to_cache ? cache_row(sb, slot, pos) : (long)n) * (sg.heads * sg.hd) + u * sg.hd;
+	float ss = 0.f;
+	for (int i = lane; i < sg.hd; i += 32) {
+		const int ch = sg.col + u * sg.hd + i;
+		float y = 0.f;
+		for (int j = 0; j < a.taps; ++j) {
+			const int ago = T1 - j; // tap j multiplies the value `ago` positions back
+			const float v = ago <= back ? a.proj[(size_t)(n - ago) * a.ldp + ch] : st[(size_t)(T1 - (ago - back)) * a.channels + ch];
+			y += ldf(a.w + (size_t)ch * a.taps + j) * v;
+		}
+		if (sg.act) y = y * sigmoidf_(y);
+		d[i] = y;
+		ss += y * y;
+	}
+	if (sg.norm) {
+		ss = warp_sum(ss);
+		const float r = (sg.norm == 1 ? 1.f / sqrtf(ss + 1e-6f) : 1.f / sqrtf(ss / (float)sg.hd + a.eps)) * sg.mul;
+		for (int i = lane; i < sg.hd; i += 32) d[i] *= r;
+	}
+}
+// after the convolution: the state becomes the last taps-1 projected values of each sequence
+__global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int taps, int channels, SeqBatch sb) {
+	const int b = blockIdx.y, ch = blockIdx.x * blockDim.x + threadIdx.x;
+	if (ch >= channels) return;
+	const int T1 = taps - 1, cnt = sb.scount[b], start = sb.sstart[b];
+	float* st = state + (size_t)sb.sslot[b] * T1 * channels;
+	for (int i = 0; i < T1; ++i) { // new[i] = value T1 - i positions before the end; ascending i only reads old[i + cnt] with cnt >= 1
+		const int ago = T1 - i;
+		st[(size_t)i * channels + ch] = ago <= cnt ? proj[(size_t)(start + cnt - ago) * ldp + ch] : st[(size_t)(i + cnt) * channels + ch];
+	}
+}
+
+// ---------------------------------------------------------------- attention over the paged cache
+// One CTA per (token, tile of query heads that share one key/value head).  Keys: `kd` floats at column kcol of the K cache
+// rows, values: `vd` floats at column vcol of the V cache rows (latent attention: both are the cached latent).  Softmax in
+// fp32, online over chunks of ATT_KC keys; `sink` joins the denominator only; `gate` (raw, per token and head) multiplies
+// the output through a sigmoid.
+#define ATT_KC 64
+#define ATT_THREADS 256
+#define ATT_MAXI 32 // output elements per thread
+struct AttArgs {
+	const float* q;   // [N][heads][kd]
+	const float* kc;  // cache rows of width kld
+	const float* vc;
+	int kld, vld;
+	int heads, group; // query heads per key/value head
+	int tile;         // query heads per CTA (divides group)
+	int kd, vd;
+	int window;       // <= 0: all earlier positions
+	float scale;
+	const bf16* sink; // [heads] or null
+	const float* gate;
+	int ldg;          // gate[n * ldg + h]
+};
+template <typename AT>
+__global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* out, SeqBatch sb) {
+	extern __shared__ float sm[];
+	const int n = blockIdx.x, h0 = blockIdx.y * a.tile, R = a.tile;
+	const int kvh = h0 / a.group;
+	float* qs = sm;                  // [R][kd]
+	float* sc = qs + R * a.kd;       // [R][ATT_KC]
+	float* mrow = sc + R * ATT_KC;   // [R] running maximum
+	float* lrow = mrow + R;          // [R] running denominator
+	float* frow = lrow + R;          // [R] rescale factor of this chunk
+	__shared__ long rows[ATT_KC];    // cache rows of this chunk's keys
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = ATT_THREADS / 32;
+	const int slot = sb.tslot[n], pos = sb.tpos[n];
+	const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+	for (int i = tid; i < R * a.kd; i += ATT_THREADS) qs[i] = a.q[((size_t)n * a.heads + h0) * a.kd + i];
+	if (tid < R) {
+		const float s = a.sink ? ldf(a.sink + h0 + tid) : -INFINITY;
+		mrow[tid] = s, lrow[tid] = a.sink ? 1.f : 0.f;
+	}
+	float acc[ATT_MAXI];
+#pragma unroll
+	for (int i = 0; i < ATT_MAXI; ++i) acc[i] = 0.f;
+	const int items = R * a.vd;
+	__syncthreads();
+	for (int c0 = lo; c0 <= pos; c0 += ATT_KC) {
+		const int nk = min(ATT_KC, pos - c0 + 1);
+		if (tid < ATT_KC) rows[tid] = tid < nk ? cache_row(sb, slot, c0 + tid) : 0;
+		__syncthreads();
+		// scores: one warp per key, lanes across the key's channels
+		for (int j = warp; j < ATT_KC; j += nwarp) {
+			if (j < nk) {
+				const float* kr = a.kc + rows[j] * a.kld + (size_t)kvh * a.kd;
+				for (int r = 0; r < R; ++r) {
+					float d = 0.f;
+					for (int i = lane; i < a.kd; i += 32) d += qs[r * a.kd + i] * kr[i];
+					d = warp_sum(d);
+					if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+				}
+			} else if (lane == 0) {
+				for (int r = 0; r < R; ++r) sc[r * ATT_KC + j] = -INFINITY;
+			}
+		}
+		__syncthreads();
+		// running maximum, probabilities in place, denominator
+		for (int r = warp; r < R; r += nwarp) {
+			float mx = -INFINITY;
+			for (int j = lane; j < ATT_KC; j += 32) mx = fmaxf(mx, sc[r * ATT_KC + j]);
+			mx = warp_max(mx);
+			const float mo = mrow[r], mn = fmaxf(mo, mx);
+			float ps = 0.f;
+			for (int j = lane; j < ATT_KC; j += 32) {
+				const float p = expf(sc[r * ATT_KC + j] - mn);
+				sc[r * ATT_KC + j] = p, ps += p;
+			}
+			ps = warp_sum(ps);
+			if (lane == 0) {
+				const float f = mo == -INFINITY ? 0.f : expf(mo - mn);
+				frow[r] = f, lrow[r] = lrow[r] * f + ps, mrow[r] = mn;
+			}
+		}
+		__syncthreads();
+		// values
+#pragma unroll
+		for (int k = 0; k < ATT_MAXI; ++k) {
+			const int it = tid + k * ATT_THREADS;
+			if (it < items) {
+				const int r = it / a.vd, d = it % a.vd;
+				float s = acc[k] * frow[r];
+				for (int j = 0; j < nk; ++j) s += sc[r * ATT_KC + j] * a.vc[rows[j] * a.vld + (size_t)kvh * a.vd + d];
+				acc[k] = s;
+			}
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int k = 0; k < ATT_MAXI; ++k) {
+		const int it = tid + k * ATT_THREADS;
+		if (it < items) {
+			const int r = it / a.vd, d = it % a.vd;
+			float v = acc[k] / lrow[r];
+			if (a.gate) v *= sigmoidf_(a.gate[(size_t)n * a.ldg + h0 + r]);
+			out[((size_t)n * a.heads + h0 + r) * a.vd + d] = to_act<AT>(v);
+		}
+	}
+}
+
+// ---------------------------------------------------------------- gated delta rule
+// One CTA per (sequence, head): the head's state S [dim][vdim] sits in shared memory for all tokens of the step, thread j
+// owns value column j.  Per token:  S <- g (.) S (rows);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+// g = exp(-exp(A_log) softplus(dt + dt_bias)) and beta = sigmoid(.) are formed here in fp32.
+struct DeltaArgs {
+	const float *q, *k, *v; // [N][kv_heads*dim] x2, [N][heads*vdim]
+	const float* proj;      // beta (raw) at column bcol
+	int ldp, bcol;
+	const float* dt;        // [N][heads*dim] raw
+	const bf16 *a_log, *dt_bias;
+	float* state;           // [slots][heads][dim][vdim]
+	float* o;               // [N][heads*vdim]
+	int heads, kv_heads, dim, vdim;
+};
+__global__ void k_seq_delta_scan(DeltaArgs a, SeqBatch sb) {
+	extern __shared__ float sm[];
+	const int b = blockIdx.x, h = blockIdx.y, D = a.dim, V = a.vdim;
+	const int kh = h / (a.heads / a.kv_heads);
+	float* S = sm;          // [D][V]
+	float* ks = S + D * V;  // [D]
+	float* qs = ks + D;
+	float* gs = qs + D;
+	const int tid = threadIdx.x;
+	float* Sg = a.state + ((size_t)sb.sslot[b] * a.heads + h) * D * V;
+	for (int i = tid; i < D * V; i += blockDim.x) S[i] = Sg[i];
+	const float A = expf(ldf(a.a_log + h));
+	const int start = sb.sstart[b], cnt = sb.scount[b];
+	for (int t = 0; t < cnt; ++t) {
+		const int n = start + t;
+		__syncthreads();
+		for (int i = tid; i < D; i += blockDim.x) {
+			ks[i] = a.k[((size_t)n * a.kv_heads + kh) * D + i];
+			qs[i] = a.q[((size_t)n * a.kv_heads + kh) * D + i];
+			gs[i] = expf(-A * softplusf_(a.dt[((size_t)n * a.heads + h) * D + i] + ldf(a.dt_bias + h * D + i)));
+		}
+		__syncthreads();
+		if (tid < V) {
+			float dot = 0.f;
+			for (int i = 0; i < D; ++i) {
+				const float s = gs[i] * S[i * V + tid];
+				S[i * V + tid] = s;
+				dot += s * ks[i];
+			}
+			const float beta = sigmoidf_(a.proj[(size_t)n * a.ldp + a.bcol + h]);
+			const float u = beta * (a.v[((size_t)n * a.heads + h) * V + tid] - dot);
+			float o = 0.f;
+			for (int i = 0; i < D; ++i) {
+				const float s = S[i * V + tid] + ks[i] * u;
+				S[i * V + tid] = s;
+				o += s * qs[i];
+			}
+			a.o[((size_t)n * a.heads + h) * V + tid] = o;
+		}
+	}
+	__syncthreads();
+	for (int i = tid; i < D * V; i += blockDim.x) Sg[i] = S[i];
+}
+// read-out: o / rms(o) (per head) * w * sigmoid(gate); one warp per (token, head)
+template <typename AT>
+__global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, const bf16* w, int N, int heads, int vdim, float eps) {
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
+	if (u >= (size_t)N * heads) return;
+	const float* src = o + u * vdim;
+	float ss = 0.f;
+	for (int i = lane; i < vdim; i += 32) ss += src[i] * src[i];
+	ss = warp_sum(ss);
+	const float r = 1.f / sqrtf(ss / (float)vdim + eps);
+	for (int i = lane; i < vdim; i += 32) out[u * vdim + i] = to_act<AT>(src[i] * r * ldf(w + i) * sigmoidf_(gate[u * vdim + i]));
+}
+
+// ---------------------------------------------------------------- products  Y[n][m] = sum_k X[n][k] W[m][k]
+// blockIdx.z = batch (per-head products): X, W, Y advance by xbs, wbs, ybs elements.
+enum { EPI_F32 = 0, EPI_ACT = 1, EPI_DYT_RES = 2 };
+struct GemmArgs {
+	const void* X;
+	long ldx, xbs;
+	const bf16* W;
+	long ldw, wbs;
+	void* Y;
+	long ldy, ybs;
+	int N, M, K;
+	int epi;                 // EPI_F32: Y fp32; EPI_ACT: Y of the activation type; EPI_DYT_RES: Y fp32 residual += tanh(alpha acc) w + b
+	const bf16 *nw, *nb, *na;
+};
+template <typename AT>
+__device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, int n, int m, float acc) {
+	if (n >= a.N || m >= a.M) return;
+	const size_t o = (size_t)z * a.ybs + (size_t)n * a.ldy + m;
+	if (a.epi == EPI_F32) ((float*)a.Y)[o] = acc;
+	else if (a.epi == EPI_ACT) ((AT*)a.Y)[o] = to_act<AT>(acc);
+	else ((float*)a.Y)[o] += tanhf(ldf(a.na) * acc) * ldf(a.nw + m) + ldf(a.nb + m);
+}
+
+// exact mode: fp32 FMA, 64 x 64 tile, 16-deep steps, 256 threads with 4 x 4 outputs each
+__global__ void __launch_bounds__(256) k_seq_gemm_f32(GemmArgs a) {
+	__shared__ float Xs[16][64 + 4], Ws[16][64 + 4];
+	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
+	const float* X = (const float*)a.X + (size_t)z * a.xbs;
+	const bf16* W = a.W + (size_t)z * a.wbs;
+	const int tn = (tid / 16) * 4, tm = (tid % 16) * 4;
+	float acc[4][4] = {};
+	for (int k0 = 0; k0 < a.K; k0 += 16) {
+		for (int i = tid; i < 64 * 16; i += 256) {
+			const int r = i / 16, k = i % 16;
+			Xs[k][r] = (n0 + r < a.N && k0 + k < a.K) ? X[(size_t)(n0 + r) * a.ldx + k0 + k] : 0.f;
+			Ws[k][r] = (m0 + r < a.M && k0 + k < a.K) ? ldf(W + (size_t)(m0 + r) * a.ldw + k0 + k) : 0.f;
+		}
+		__syncthreads();
+#pragma unroll
+		for (int k = 0; k < 16; ++k) {
+			float xv[4], wv[4];
+#pragma unroll
+			for (int i = 0; i < 4; ++i) xv[i] = Xs[k][tn + i], wv[i] = Ws[k][tm + i];
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int i = 0; i < 4; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j) gemm_store<float>(a, z, n0 + tn + i, m0 + tm + j, acc[i][j]);
+}
+
+// bf16 x bf16 -> fp32 on the tensor cores for ANY shape (edges are zero-filled in shared memory): 64 tokens x 64 rows per
+// CTA, 32-deep steps, four warps of 32 x 32.  The tcgen05 kernel below takes the shapes that fill its tiles.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&A)[4], const uint32_t (&B)[2]) {
+	asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+	             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+	             : "r"(A[0]), "r"(A[1]), "r"(A[2]), "r"(A[3]), "r"(B[0]), "r"(B[1]));
+}
+#define GB_LD 40 // bf16 per shared-memory row: 32 + 8 keeps the fragment reads conflict-free
+__device__ __forceinline__ void gemm_fill_tile(bf16 (*dst)[GB_LD], const bf16* src, long ld, int r0, int rows, int k0, int K, int tid) {
+	// 64 rows x 32 columns as 256 groups of 8: two per thread
+	for (int i = tid; i < 256; i += 128) {
+		const int r = i >> 2, c = (i & 3) * 8;
+		const bf16* p = src + (size_t)(r0 + r) * ld + k0 + c;
+		uint4 v = make_uint4(0, 0, 0, 0);
+		if (r0 + r < rows) {
+			if (k0 + c + 8 <= K && (((uintptr_t)p) & 15) == 0) v = *(const uint4*)p;
+			else {
+				bf16 t[8];
+#pragma unroll
+				for (int e = 0; e < 8; ++e) t[e] = k0 + c + e < K ? p[e] : __float2bfloat16_rn(0.f);
+				v = *(const uint4*)t;
+			}
+		}
+		*(uint4*)&dst[r][c] = v;
+	}
+}
+__global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
+	__shared__ __align__(16) bf16 Xs[64][GB_LD], Ws[64][GB_LD];
+	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
+	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
+	const bf16* W = a.W + (size_t)z * a.wbs;
+	const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+	const int wn = (warp >> 1) * 32, wm = (warp & 1) * 32;
+	float acc[2][4][4] = {};
+	for (int k0 = 0; k0 < a.K; k0 += 32) {
+		gemm_fill_tile(Xs, X, a.ldx, n0, a.N, k0, a.K, tid);
+		gemm_fill_tile(Ws, W, a.ldw, m0, a.M, k0, a.K, tid);
+		__syncthreads();
+#pragma unroll
+		for (int kk = 0; kk < 32; kk += 16) {
+			uint32_t A[2][4], B[4][2];
+#pragma unroll
+			for (int i = 0; i < 2; ++i) {
+				const int r = wn + i * 16 + g;
+				A[i][0] = *(const uint32_t*)&Xs[r][kk + 2 * t], A[i][1] = *(const uint32_t*)&Xs[r + 8][kk + 2 * t];
+				A[i][2] = *(const uint32_t*)&Xs[r][kk + 2 * t + 8], A[i][3] = *(const uint32_t*)&Xs[r + 8][kk + 2 * t + 8];
+			}
+#pragma unroll
+			for (int j = 0; j < 4; ++j) {
+				const int r = wm + j * 8 + g;
+				B[j][0] = *(const uint32_t*)&Ws[r][kk + 2 * t], B[j][1] = *(const uint32_t*)&Ws[r][kk + 2 * t + 8];
+			}
+#pragma unroll
+			for (int i = 0; i < 2; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], A[i], B[j]);
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int i = 0; i < 2; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int n = n0 + wn + i * 16 + g, m = m0 + wm + j * 8 + 2 * t;
+			gemm_store<bf16>(a, z, n, m, acc[i][j][0]), gemm_store<bf16>(a, z, n, m + 1, acc[i][j][1]);
+			gemm_store<bf16>(a, z, n + 8, m, acc[i][j][2]), gemm_store<bf16>(a, z, n + 8, m + 1, acc[i][j][3]);
+		}
+}
+
+// ---------------------------------------------------------------- sampling helper
+__global__ void k_seq_argmax(const float* logits, int vocab, int* out) {
+	__shared__ float bv[32];
+	__shared__ int bi[32];
+	const float* row = logits + (size_t)blockIdx.x * vocab;
+	float v = -INFINITY;
+	int ix = 0x7fffffff;
+	for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+		if (row[i] > v) v = row[i], ix = i; // ascending i per thread: the first maximum stays
+	for (int o = 16; o > 0; o >>= 1) {
+		const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+		const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+		if (ov > v || (ov == v && oi < ix)) v = ov, ix = oi;
+	}
+	if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = v, bi[threadIdx.x >> 5] = ix;
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+			if (bv[w] > v || (bv[w] == v && bi[w] < ix)) v = bv[w], ix = bi[w];
+		out[blockIdx.x] = ix;
+	}
+}

@@ -1,0 +1,555 @@
+// seqmodel.cu -- host side of libcalm_b200_seq.so (include/calm_b200_seq.h): the state manager (sequence slots, a paged
+// cache shared by every position-indexed cache of the model, per-slot recurrent and convolution state) and the step
+// function that runs a packed batch of tokens through the layer list.
+
+#include "../../include/calm_b200_seq.h"
+
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "seqkernels.cuh"
+#include "seqgemm_tc.cuh"
+
+namespace {
+
+uint64_t g_seq_launches = 0;
+
+enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_COUNT };
+const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise"};
+
+// what one run of a layer owns (a looped layer has one of these per pass)
+struct RunState {
+	int layer = 0;
+	bool readd = false;      // the embedding output is added to the stream right before this run
+	float* cache_a = nullptr; // SEQ_LATENT: latent rows; SEQ_WINDOW: key rows
+	float* cache_b = nullptr; // SEQ_WINDOW: value rows
+	float* conv = nullptr;    // [slots][taps-1][channels]
+	float* delta = nullptr;   // [slots][heads][dim][vdim]
+	size_t conv_per_slot = 0, delta_per_slot = 0;
+};
+
+struct Slot {
+	bool open = false;
+	int len = 0;
+	std::vector<int> pages;
+};
+
+struct Seq {
+	SeqModel m;
+	std::vector<SeqLayer> layers;
+	std::vector<RunState> runs;
+	cudaStream_t stream = nullptr;
+	int sms = 0;
+	bool tc = false; // tcgen05 products available (bf16 mode)
+
+	// state manager
+	int n_pages = 0, max_pages = 0;
+	std::vector<int> free_pages;
+	std::vector<Slot> slots;
+	std::vector<int> table; // host mirror of the page table
+	int* table_dev = nullptr;
+
+	// per-step batch description
+	int cap_tokens = 0, cap_seqs = 0, cap_want = 0;
+	int *d_tok = nullptr, *d_tslot = nullptr, *d_tpos = nullptr, *d_tfirst = nullptr, *d_sstart = nullptr, *d_scount = nullptr, *d_spos0 = nullptr, *d_sslot = nullptr,
+	    *d_want = nullptr, *d_argmax = nullptr;
+	std::vector<int> h_meta;
+
+	// workspace for cap_tokens tokens
+	float *x = nullptr, *x0 = nullptr, *proj = nullptr, *f[6] = {};
+	void *hA = nullptr, *a1 = nullptr, *a2 = nullptr; // activation type (float or bf16)
+	size_t w_proj = 0, w_f = 0, w_a = 0;              // widths (elements per token)
+	float* logits = nullptr;
+	void* hW = nullptr; // normed rows of the wanted tokens
+	int last_want = 0, last_tokens = 0;
+
+	bool trace = false;
+	float* trace_buf = nullptr;
+	int trace_cap = 0;
+
+	bool perf = false;
+	double kind_ms[KD_COUNT] = {}, kind_bytes[KD_COUNT] = {}, kind_flops[KD_COUNT] = {};
+	long kind_launches[KD_COUNT] = {};
+	cudaEvent_t ev[2] = {nullptr, nullptr}, timer[2] = {nullptr, nullptr};
+};
+
+void* dalloc(size_t bytes) {
+	void* p = nullptr;
+	CUDA_CHECK(cudaMalloc(&p, bytes ? bytes : 16));
+	return p;
+}
+int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
+size_t act_size(const Seq& s) { return s.m.exact ? sizeof(float) : sizeof(bf16); }
+
+// every launch goes through here: counts it and, while profiling, brackets it with events
+template <typename F>
+void run_kernel(Seq& s, int kind, double bytes, double flops, F&& launch) {
+	if (s.perf) CUDA_CHECK(cudaEventRecord(s.ev[0], s.stream));
+	launch();
+	CUDA_CHECK(cudaGetLastError());
+	++g_seq_launches;
+	if (s.perf) {
+		CUDA_CHECK(cudaEventRecord(s.ev[1], s.stream));
+		CUDA_CHECK(cudaEventSynchronize(s.ev[1]));
+		float ms = 0;
+		CUDA_CHECK(cudaEventElapsedTime(&ms, s.ev[0], s.ev[1]));
+		s.kind_ms[kind] += ms, s.kind_bytes[kind] += bytes, s.kind_flops[kind] += flops, ++s.kind_launches[kind];
+	}
+}
+
+size_t in_rows(const SeqLayer& L) {
+	switch (L.type) {
+	case SEQ_LATENT: return (size_t)L.q_rank + L.kv_rank + L.heads;
+	case SEQ_DELTA: return (size_t)2 * L.kv_heads * L.dim + (size_t)L.heads * L.vdim + L.heads + L.a_rank + L.g_rank;
+	default: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim;
+	}
+}
+int conv_channels(const SeqLayer& L) {
+	if (L.type == SEQ_DELTA) return 2 * L.kv_heads * L.dim + L.heads * L.vdim;
+	if (L.type == SEQ_WINDOW) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim;
+	return 0;
+}
+// query heads per CTA of the attention kernel: divides the group, keeps the accumulators in registers and the queries in shared memory
+int attn_tile(int group, int kd, int vd) {
+	int t = group;
+	while (t > 1 && ((size_t)t * vd > (size_t)ATT_MAXI * ATT_THREADS || (size_t)t * (kd + ATT_KC + 3) * sizeof(float) > 96 * 1024 || t > 16)) {
+		int d = t - 1;
+		while (group % d) --d;
+		t = d;
+	}
+	return t;
+}
+size_t attn_smem(int tile, int kd) { return (size_t)tile * (kd + ATT_KC + 3) * sizeof(float); }
+
+void validate(const Seq& s) {
+	const SeqModel& m = s.m;
+	if (m.vocab < 1 || m.width < 1 || m.n_layers < 1) CALM_FATAL("seq: empty model");
+	if (m.page < 1 || m.max_seqs < 1 || m.max_tokens < 1) CALM_FATAL("seq: page, max_seqs and max_tokens must be positive");
+	if (m.loop_times > 1 && !(0 <= m.loop_start && m.loop_start < m.loop_stop && m.loop_stop <= m.n_layers)) CALM_FATAL("seq: bad loop span");
+	for (int i = 0; i < m.n_layers; ++i) {
+		const SeqLayer& L = s.layers[i];
+		if (L.heads < 1 || L.dim < 1 || L.vdim < 1) CALM_FATAL("seq: layer %d: heads, dim and vdim must be positive", i);
+		if (L.type == SEQ_LATENT) {
+			if (L.q_rank < 1 || L.kv_rank < 1) CALM_FATAL("seq: layer %d: latent ranks must be positive", i);
+			if ((size_t)L.kv_rank > (size_t)ATT_MAXI * ATT_THREADS) CALM_FATAL("seq: layer %d: kv_rank %d is more than the attention kernel holds", i, L.kv_rank);
+		} else if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW) {
+			if (L.kv_heads < 1 || L.heads % L.kv_heads) CALM_FATAL("seq: layer %d: heads must be a multiple of kv_heads", i);
+			if (L.taps < 1) CALM_FATAL("seq: layer %d: taps must be positive", i);
+			if (L.type == SEQ_DELTA) {
+				if (L.vdim > 1024) CALM_FATAL("seq: layer %d: vdim above 1024", i);
+				if (((size_t)L.dim * L.vdim + 3 * (size_t)L.dim) * sizeof(float) > 227 * 1024) CALM_FATAL("seq: layer %d: a %d x %d state does not fit shared memory", i, L.dim, L.vdim);
+				if (L.a_rank < 1 || L.g_rank < 1) CALM_FATAL("seq: layer %d: decay and gate ranks must be positive", i);
+			} else if ((size_t)L.vdim > (size_t)ATT_MAXI * ATT_THREADS) CALM_FATAL("seq: layer %d: vdim too large", i);
+		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
+	}
+}
+
+void reserve_tokens(Seq& s, int N, int B, int W) {
+	if (B > s.cap_seqs || N > s.cap_tokens) {
+		const int cn = std::max(N, s.cap_tokens), cb = std::max(B, s.cap_seqs);
+		CUDA_CHECK(cudaStreamSynchronize(s.stream));
+		cudaFree(s.d_tok);
+		s.d_tok = (int*)dalloc(((size_t)4 * cn + 4 * cb) * sizeof(int));
+		s.d_tslot = s.d_tok + cn, s.d_tpos = s.d_tslot + cn, s.d_tfirst = s.d_tpos + cn;
+		s.d_sstart = s.d_tfirst + cn, s.d_scount = s.d_sstart + cb, s.d_spos0 = s.d_scount + cb, s.d_sslot = s.d_spos0 + cb;
+		s.cap_seqs = cb;
+	}
+	if (W > s.cap_want) {
+		CUDA_CHECK(cudaStreamSynchronize(s.stream));
+		cudaFree(s.d_want), cudaFree(s.d_argmax), cudaFree(s.logits), cudaFree(s.hW);
+		s.cap_want = std::max(W, 2 * s.cap_want);
+		s.d_want = (int*)dalloc(s.cap_want * sizeof(int));
+		s.d_argmax = (int*)dalloc(s.cap_want * sizeof(int));
+		s.logits = (float*)dalloc((size_t)s.cap_want * s.m.vocab * sizeof(float));
+		s.hW = dalloc((size_t)s.cap_want * s.m.width * act_size(s));
+	}
+	if (N > s.cap_tokens) {
+		const size_t cn = N;
+		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2);
+		for (float*& p : s.f) cudaFree(p);
+		s.x = (float*)dalloc(cn * s.m.width * sizeof(float));
+		s.x0 = (float*)dalloc(cn * s.m.width * sizeof(float));
+		s.proj = (float*)dalloc(cn * s.w_proj * sizeof(float));
+		for (float*& p : s.f) p = (float*)dalloc(cn * s.w_f * sizeof(float));
+		s.hA = dalloc(cn * s.m.width * act_size(s));
+		s.a1 = dalloc(cn * s.w_a * act_size(s));
+		s.a2 = dalloc(cn * s.w_a * act_size(s));
+		s.cap_tokens = N;
+	}
+	if (s.trace && (size_t)N * s.runs.size() > (size_t)s.trace_cap) {
+		cudaFree(s.trace_buf);
+		s.trace_cap = N * (int)s.runs.size();
+		s.trace_buf = (float*)dalloc((size_t)s.trace_cap * s.m.width * sizeof(float));
+	}
+}
+
+// ---------------------------------------------------------------- launches
+
+void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
+          const SeqNorm* nrm = nullptr) {
+	GemmArgs a;
+	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
+	a.N = N, a.M = M, a.K = K, a.epi = epi;
+	a.nw = nrm ? (const bf16*)nrm->w : nullptr, a.nb = nrm ? (const bf16*)nrm->b : nullptr, a.na = nrm ? (const bf16*)nrm->alpha : nullptr;
+	const double flops = 2.0 * N * M * K * batch;
+	const double bytes = ((double)M * K * 2 + (double)N * K * act_size(s) + (double)N * M * 4) * batch;
+	if (s.tc && gemm_tc_fits(a, batch)) {
+		run_kernel(s, KD_GEMM_TC, bytes, flops, [&] { gemm_tc_launch(a, s.stream); });
+		return;
+	}
+	const dim3 grid(cdiv(M, 64), cdiv(N, 64), batch);
+	run_kernel(s, KD_GEMM, bytes, flops, [&] {
+		if (s.m.exact) k_seq_gemm_f32<<<grid, 256, 0, s.stream>>>(a);
+		else k_seq_gemm_bf16<<<grid, 128, 0, s.stream>>>(a);
+	});
+}
+
+void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R) {
+	const size_t n = (size_t)R * s.m.width;
+	run_kernel(s, KD_NORM, n * (4 + act_size(s)), 0, [&] {
+		if (s.m.exact) k_seq_dyt<float><<<cdiv(n, 256), 256, 0, s.stream>>>((float*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
+		else k_seq_dyt<bf16><<<cdiv(n, 256), 256, 0, s.stream>>>((bf16*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
+	});
+}
+
+void attention(Seq& s, int kind, const AttArgs& a, void* out, const SeqBatch& sb, double kv_rows) {
+	const size_t smem = attn_smem(a.tile, a.kd);
+	const dim3 grid(sb.N, a.heads / a.tile);
+	const double bytes = kv_rows * (a.heads / a.group) * (a.kc == a.vc ? a.kd : a.kd + a.vd) * 4.0;
+	const double flops = 2.0 * kv_rows * a.heads * (a.kd + a.vd);
+	run_kernel(s, kind, bytes, flops, [&] {
+		if (s.m.exact) k_seq_attention<float><<<grid, ATT_THREADS, smem, s.stream>>>(a, (float*)out, sb);
+		else k_seq_attention<bf16><<<grid, ATT_THREADS, smem, s.stream>>>(a, (bf16*)out, sb);
+	});
+}
+
+void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& sb) {
+	const int units = ca.seg[0].heads + ca.seg[1].heads + ca.seg[2].heads;
+	ca.proj = s.proj, ca.ldp = (int)in_rows(L), ca.w = (const bf16*)L.conv, ca.taps = L.taps, ca.channels = conv_channels(L), ca.state = r.conv, ca.eps = s.m.eps;
+	const double bytes = (double)sb.N * ca.channels * 8;
+	run_kernel(s, KD_CONV, bytes, 0, [&] { k_seq_conv_heads<<<dim3(sb.N, cdiv(units, 4)), 128, 0, s.stream>>>(ca, sb); });
+	if (L.taps > 1)
+		run_kernel(s, KD_CONV, 0, 0, [&] { k_seq_conv_state<<<dim3(cdiv(ca.channels, 128), sb.B), 128, 0, s.stream>>>(r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb); });
+}
+
+template <typename AT>
+void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows) {
+	const int N = sb.N, W = s.m.width, P = (int)in_rows(L);
+	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
+	gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, P, W, 1, EPI_F32);
+	if (L.type == SEQ_LATENT) {
+		const int H = L.heads, D = L.dim, Dv = L.vdim, Rq = L.q_rank, Rk = L.kv_rank;
+		RmsSeg sq{0, Rq, (const bf16*)L.dq_norm}, sc{Rq, Rk, (const bf16*)L.dkv_norm};
+		run_kernel(s, KD_NORM, (double)N * (Rq + Rk) * 8, 0,
+		           [&] { k_seq_latent_norm<AT><<<dim3(cdiv(N, 4), 2), 128, 0, s.stream>>>(s.proj, P, sq, sc, a1, r.cache_a, sb, s.m.eps); });
+		gemm(s, a1, Rq, 0, L.w_uq, Rq, 0, a2, (long)H * D, 0, N, H * D, Rq, 1, EPI_ACT);
+		// the key up-projection moves to the query side: q'_h = W_uk,h^T q_h, so scores and values are taken on the cached latent itself
+		gemm(s, a2, (long)H * D, D, L.w_ukT, D, (long)Rk * D, s.f[0], (long)H * Rk, Rk, N, Rk, D, H, EPI_F32);
+		AttArgs a;
+		a.q = s.f[0], a.kc = a.vc = r.cache_a, a.kld = a.vld = Rk, a.heads = H, a.group = H, a.tile = attn_tile(H, Rk, Rk), a.kd = a.vd = Rk, a.window = 0;
+		a.scale = L.scale, a.sink = nullptr, a.gate = s.proj + Rq + Rk, a.ldg = P;
+		attention(s, KD_ATTN_LATENT, a, a1, sb, kv_rows);
+		gemm(s, a1, (long)H * Rk, Rk, L.w_uv, Rk, (long)Dv * Rk, a2, (long)H * Dv, Dv, N, Dv, Rk, H, EPI_ACT);
+		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+	} else if (L.type == SEQ_DELTA) {
+		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
+		const int cq = 0, ck = G * D, cv = 2 * G * D, cb = cv + H * Dv, ca1 = cb + H, cg1 = ca1 + L.a_rank;
+		ConvArgs ca;
+		ca.seg[0] = ConvSeg{cq, G, D, 1, 1, 1.f / sqrtf((float)D), 0, s.f[0]};
+		ca.seg[1] = ConvSeg{ck, G, D, 1, 1, 1.f, 0, s.f[1]};
+		ca.seg[2] = ConvSeg{cv, H, Dv, 1, 0, 1.f, 0, s.f[2]};
+		conv(s, L, r, ca, sb);
+		const int lr = L.a_rank + L.g_rank;
+		run_kernel(s, KD_ELEMENT, (double)N * lr * 6, 0, [&] { k_seq_cast_cols<AT><<<cdiv((long)N * lr, 256), 256, 0, s.stream>>>(a1, s.proj, P, ca1, lr, N); });
+		gemm(s, a1, lr, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_F32);
+		gemm(s, a1 + L.a_rank, lr, 0, L.w_g2, L.g_rank, 0, s.f[4], (long)H * Dv, 0, N, H * Dv, L.g_rank, 1, EPI_F32);
+		(void)cg1;
+		DeltaArgs d;
+		d.q = s.f[0], d.k = s.f[1], d.v = s.f[2], d.proj = s.proj, d.ldp = P, d.bcol = cb, d.dt = s.f[3], d.a_log = (const bf16*)L.a_log, d.dt_bias = (const bf16*)L.dt_bias;
+		d.state = r.delta, d.o = s.f[5], d.heads = H, d.kv_heads = G, d.dim = D, d.vdim = Dv;
+		const size_t smem = ((size_t)D * Dv + 3 * D) * sizeof(float);
+		const int threads = std::max(64, cdiv(Dv, 32) * 32);
+		run_kernel(s, KD_DELTA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 6.0,
+		           [&] { k_seq_delta_scan<<<dim3(sb.B, H), threads, smem, s.stream>>>(d, sb); });
+		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
+		           [&] { k_seq_delta_out<AT><<<cdiv((long)N * H, 4), 128, 0, s.stream>>>(a2, s.f[5], s.f[4], (const bf16*)L.out_norm, N, H, Dv, s.m.eps); });
+		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+	} else {
+		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
+		ConvArgs ca;
+		ca.seg[0] = ConvSeg{0, H, D, 0, 2, 1.f, 0, s.f[0]};
+		ca.seg[1] = ConvSeg{H * D, G, D, 0, 2, 1.f, 1, r.cache_a};
+		ca.seg[2] = ConvSeg{H * D + G * D, G, Dv, 0, 0, 1.f, 1, r.cache_b};
+		conv(s, L, r, ca, sb);
+		AttArgs a;
+		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
+		a.window = L.window, a.scale = L.scale, a.sink = (const bf16*)L.sink, a.gate = nullptr, a.ldg = 0;
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * L.window) : kv_rows);
+		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+	}
+	if (L.ff > 0) {
+		dyt(s, s.hA, s.x, nullptr, L.norm2, N);
+		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
+		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
+		           [&] { k_seq_ff_act<AT><<<cdiv((long)N * L.ff, 256), 256, 0, s.stream>>>(a2, s.proj, L.ff, N, L.limit); });
+		gemm(s, a2, L.ff, 0, L.w_down, L.ff, 0, s.x, W, 0, N, W, L.ff, 1, EPI_DYT_RES, &L.norm2b);
+	}
+}
+
+} // namespace
+
+// ---------------------------------------------------------------- C ABI
+
+extern "C" void* calm_b200_seq_upload(const void* host, size_t size) {
+	void* p = dalloc(size);
+	CUDA_CHECK(cudaMemcpy(p, host, size, cudaMemcpyHostToDevice));
+	return p;
+}
+extern "C" void calm_b200_seq_free(void* p) { cudaFree(p); }
+extern "C" uint64_t calm_b200_seq_launch_count(void) { return g_seq_launches; }
+
+extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
+	int count = 0;
+	if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) CALM_FATAL("no CUDA device available; this backend has no CPU fallback");
+	Seq* sp = new Seq;
+	Seq& s = *sp;
+	s.m = *model;
+	s.layers.assign(model->layers, model->layers + model->n_layers);
+	s.m.layers = s.layers.data();
+	validate(s);
+	int dev = 0;
+	CUDA_CHECK(cudaGetDevice(&dev));
+	cudaDeviceProp prop;
+	CUDA_CHECK(cudaGetDeviceProperties(&prop, dev));
+	if (prop.major != 10) CALM_FATAL("device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+	s.sms = prop.multiProcessorCount;
+	CUDA_CHECK(cudaStreamCreate(&s.stream));
+	for (cudaEvent_t& e : s.ev) CUDA_CHECK(cudaEventCreate(&e));
+	for (cudaEvent_t& e : s.timer) CUDA_CHECK(cudaEventCreate(&e));
+	const char* tc = getenv("CALM_B200_SEQ_TC");
+	s.tc = !s.m.exact && !(tc && atoi(tc) == 0);
+	if (s.tc) gemm_tc_setup();
+
+	// order of layer runs: the looped span repeated, each pass with its own state
+	const SeqModel& m = s.m;
+	const int times = m.loop_times > 1 ? m.loop_times : 1;
+	const int ls = times > 1 ? m.loop_start : 0, le = times > 1 ? m.loop_stop : 0;
+	for (int i = 0; i < ls; ++i) s.runs.push_back(RunState{i});
+	for (int t = 0; t < times && le > ls; ++t)
+		for (int i = ls; i < le; ++i) {
+			RunState r{i};
+			r.readd = t > 0 && i == ls;
+			s.runs.push_back(r);
+		}
+	for (int i = le; i < m.n_layers; ++i) s.runs.push_back(RunState{i});
+
+	// pages: every live token, one partly filled page per sequence
+	s.n_pages = cdiv(m.max_tokens, m.page) + m.max_seqs;
+	s.max_pages = s.n_pages;
+	for (int p = s.n_pages - 1; p >= 0; --p) s.free_pages.push_back(p);
+	s.slots.resize(m.max_seqs);
+	s.table.assign((size_t)m.max_seqs * s.max_pages, 0);
+	s.table_dev = (int*)dalloc(s.table.size() * sizeof(int));
+	const size_t rows = (size_t)s.n_pages * m.page;
+	for (RunState& r : s.runs) {
+		const SeqLayer& L = s.layers[r.layer];
+		if (L.type == SEQ_LATENT) r.cache_a = (float*)dalloc(rows * L.kv_rank * sizeof(float));
+		if (L.type == SEQ_WINDOW) {
+			r.cache_a = (float*)dalloc(rows * L.kv_heads * L.dim * sizeof(float));
+			r.cache_b = (float*)dalloc(rows * L.kv_heads * L.vdim * sizeof(float));
+		}
+		if (L.type != SEQ_LATENT) {
+			r.conv_per_slot = (size_t)std::max(L.taps - 1, 0) * conv_channels(L);
+			r.conv = (float*)dalloc(r.conv_per_slot * m.max_seqs * sizeof(float));
+		}
+		if (L.type == SEQ_DELTA) {
+			r.delta_per_slot = (size_t)L.heads * L.dim * L.vdim;
+			r.delta = (float*)dalloc(r.delta_per_slot * m.max_seqs * sizeof(float));
+			const size_t smem = ((size_t)L.dim * L.vdim + 3 * L.dim) * sizeof(float);
+			if (smem > 48 * 1024) CUDA_CHECK(cudaFuncSetAttribute(k_seq_delta_scan, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+		}
+	}
+	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+	// workspace widths
+	for (const SeqLayer& L : s.layers) {
+		s.w_proj = std::max({s.w_proj, in_rows(L), (size_t)2 * L.ff});
+		size_t wf = 0, wa = (size_t)L.ff;
+		if (L.type == SEQ_LATENT) wf = (size_t)L.heads * L.kv_rank, wa = std::max({wa, (size_t)L.heads * L.kv_rank, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim, (size_t)L.q_rank});
+		if (L.type == SEQ_DELTA) wf = std::max((size_t)L.heads * L.dim, (size_t)L.heads * L.vdim), wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.a_rank + L.g_rank});
+		if (L.type == SEQ_WINDOW) wf = (size_t)L.heads * L.dim, wa = std::max(wa, (size_t)L.heads * L.vdim);
+		s.w_f = std::max(s.w_f, wf), s.w_a = std::max(s.w_a, wa);
+	}
+	return sp;
+}
+
+extern "C" void calm_b200_seq_release(void* handle) {
+	Seq* s = (Seq*)handle;
+	if (!s) return;
+	cudaStreamSynchronize(s->stream);
+	for (RunState& r : s->runs) cudaFree(r.cache_a), cudaFree(r.cache_b), cudaFree(r.conv), cudaFree(r.delta);
+	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
+	cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
+	for (float* p : s->f) cudaFree(p);
+	for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
+	for (cudaEvent_t e : s->timer) cudaEventDestroy(e);
+	cudaStreamDestroy(s->stream);
+	delete s;
+}
+
+extern "C" int calm_b200_seq_open(void* handle) {
+	Seq& s = *(Seq*)handle;
+	for (int i = 0; i < (int)s.slots.size(); ++i)
+		if (!s.slots[i].open) {
+			s.slots[i].open = true, s.slots[i].len = 0, s.slots[i].pages.clear();
+			for (RunState& r : s.runs) { // a slot that is used again starts from zero state
+				if (r.conv_per_slot) CUDA_CHECK(cudaMemsetAsync(r.conv + r.conv_per_slot * i, 0, r.conv_per_slot * sizeof(float), s.stream));
+				if (r.delta_per_slot) CUDA_CHECK(cudaMemsetAsync(r.delta + r.delta_per_slot * i, 0, r.delta_per_slot * sizeof(float), s.stream));
+			}
+			return i;
+		}
+	return -1;
+}
+
+extern "C" int calm_b200_seq_close(void* handle, int slot) {
+	Seq& s = *(Seq*)handle;
+	if (slot < 0 || slot >= (int)s.slots.size() || !s.slots[slot].open) return -3;
+	for (int p : s.slots[slot].pages) s.free_pages.push_back(p);
+	s.slots[slot].pages.clear(), s.slots[slot].open = false, s.slots[slot].len = 0;
+	return 0;
+}
+
+extern "C" int calm_b200_seq_length(void* handle, int slot) {
+	Seq& s = *(Seq*)handle;
+	return slot >= 0 && slot < (int)s.slots.size() && s.slots[slot].open ? s.slots[slot].len : -3;
+}
+extern "C" int calm_b200_seq_free_pages(void* handle) { return (int)((Seq*)handle)->free_pages.size(); }
+
+extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, const int* counts, const int* tokens, int n_want, const int* want, float* logits_host) {
+	Seq& s = *(Seq*)handle;
+	const SeqModel& m = s.m;
+	int N = 0, need = 0;
+	for (int b = 0; b < n_seq; ++b) {
+		const int sl = slots[b];
+		if (sl < 0 || sl >= (int)s.slots.size() || !s.slots[sl].open || counts[b] < 1) return -3;
+		for (int c = 0; c < b; ++c)
+			if (slots[c] == sl) return -3;
+		need += cdiv(s.slots[sl].len + counts[b], m.page) - (int)s.slots[sl].pages.size();
+		N += counts[b];
+	}
+	if (n_seq < 1) return -3;
+	for (int i = 0; i < N; ++i)
+		if (tokens[i] < 0 || tokens[i] >= m.vocab) return -3;
+	for (int i = 0; i < n_want; ++i)
+		if (want[i] < 0 || want[i] >= N) return -3;
+	if (need > (int)s.free_pages.size()) return -2;
+	reserve_tokens(s, N, n_seq, std::max(n_want, 1));
+
+	// pages for the new tokens, then the batch description
+	double kv_rows = 0; // cache rows the causal attentions read this step
+	s.h_meta.resize((size_t)4 * N + 4 * n_seq);
+	int *tok = s.h_meta.data(), *tslot = tok + N, *tpos = tslot + N, *tfirst = tpos + N, *sstart = tfirst + N, *scount = sstart + n_seq, *spos0 = scount + n_seq,
+	    *sslot = spos0 + n_seq;
+	int at = 0;
+	for (int b = 0; b < n_seq; ++b) {
+		Slot& sl = s.slots[slots[b]];
+		const size_t had = sl.pages.size();
+		while ((int)sl.pages.size() * m.page < sl.len + counts[b]) {
+			s.table[(size_t)slots[b] * s.max_pages + sl.pages.size()] = s.free_pages.back();
+			sl.pages.push_back(s.free_pages.back()), s.free_pages.pop_back();
+		}
+		if (sl.pages.size() > had) { // only the new entries of this slot's row travel
+			const size_t o = (size_t)slots[b] * s.max_pages + had;
+			CUDA_CHECK(cudaMemcpyAsync(s.table_dev + o, s.table.data() + o, (sl.pages.size() - had) * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+		}
+		sstart[b] = at, scount[b] = counts[b], spos0[b] = sl.len, sslot[b] = slots[b];
+		for (int t = 0; t < counts[b]; ++t, ++at) tok[at] = tokens[at], tslot[at] = slots[b], tpos[at] = sl.len + t, tfirst[at] = sstart[b], kv_rows += sl.len + t + 1;
+		sl.len += counts[b];
+	}
+	CUDA_CHECK(cudaMemcpyAsync(s.d_tok, tok, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_tslot, tslot, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_tpos, tpos, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_tfirst, tfirst, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_sstart, sstart, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_scount, scount, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_spos0, spos0, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_sslot, sslot, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	if (n_want) CUDA_CHECK(cudaMemcpyAsync(s.d_want, want, n_want * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	SeqBatch sb;
+	sb.tok = s.d_tok, sb.tslot = s.d_tslot, sb.tpos = s.d_tpos, sb.tfirst = s.d_tfirst, sb.sstart = s.d_sstart, sb.scount = s.d_scount, sb.spos0 = s.d_spos0, sb.sslot = s.d_sslot;
+	sb.pages = s.table_dev, sb.N = N, sb.B = n_seq, sb.max_pages = s.max_pages, sb.page = m.page;
+
+	const bool looped = m.loop_times > 1;
+	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
+	           [&] { k_seq_embed<<<N, 128, 0, s.stream>>>(s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
+	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
+		RunState& r = s.runs[ri];
+		const SeqLayer& L = s.layers[r.layer];
+		if (r.readd) {
+			const size_t n = (size_t)N * m.width;
+			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { k_seq_add<<<cdiv(n, 256), 256, 0, s.stream>>>(s.x, s.x0, n); });
+		}
+		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
+		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows);
+		else mixer_typed<bf16>(s, L, r, sb, kv_rows);
+		if (s.trace)
+			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
+	}
+	s.last_want = n_want, s.last_tokens = N;
+	if (n_want) {
+		dyt(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
+		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
+		if (logits_host) CUDA_CHECK(cudaMemcpyAsync(logits_host, s.logits, (size_t)n_want * m.vocab * sizeof(float), cudaMemcpyDeviceToHost, s.stream));
+	}
+	CUDA_CHECK(cudaStreamSynchronize(s.stream));
+	return 0;
+}
+
+extern "C" void calm_b200_seq_argmax(void* handle, int* out) {
+	Seq& s = *(Seq*)handle;
+	if (!s.last_want) return;
+	k_seq_argmax<<<s.last_want, 256, 0, s.stream>>>(s.logits, s.m.vocab, s.d_argmax);
+	CUDA_CHECK(cudaGetLastError());
+	++g_seq_launches;
+	CUDA_CHECK(cudaMemcpyAsync(out, s.d_argmax, s.last_want * sizeof(int), cudaMemcpyDeviceToHost, s.stream));
+	CUDA_CHECK(cudaStreamSynchronize(s.stream));
+}
+extern "C" const float* calm_b200_seq_device_logits(void* handle) { return ((Seq*)handle)->logits; }
+
+extern "C" void calm_b200_seq_set_trace(void* handle, int on) { ((Seq*)handle)->trace = on != 0; }
+extern "C" int calm_b200_seq_layer_runs(void* handle) { return (int)((Seq*)handle)->runs.size(); }
+extern "C" void calm_b200_seq_read_trace(void* handle, int run, float* out) {
+	Seq& s = *(Seq*)handle;
+	if (!s.trace_buf || run < 0 || run >= (int)s.runs.size()) return;
+	const size_t n = (size_t)s.last_tokens * s.m.width;
+	CUDA_CHECK(cudaMemcpy(out, s.trace_buf + run * n, n * sizeof(float), cudaMemcpyDeviceToHost));
+}
+
+extern "C" void calm_b200_seq_timer_start(void* handle) {
+	Seq& s = *(Seq*)handle;
+	CUDA_CHECK(cudaEventRecord(s.timer[0], s.stream));
+}
+extern "C" float calm_b200_seq_timer_stop(void* handle) {
+	Seq& s = *(Seq*)handle;
+	CUDA_CHECK(cudaEventRecord(s.timer[1], s.stream));
+	CUDA_CHECK(cudaEventSynchronize(s.timer[1]));
+	float ms = 0;
+	CUDA_CHECK(cudaEventElapsedTime(&ms, s.timer[0], s.timer[1]));
+	return ms;
+}
+extern "C" void calm_b200_seq_set_perf(void* handle, int on) {
+	Seq& s = *(Seq*)handle;
+	s.perf = on != 0;
+	if (on)
+		for (int k = 0; k < KD_COUNT; ++k) s.kind_ms[k] = s.kind_bytes[k] = s.kind_flops[k] = 0, s.kind_launches[k] = 0;
+}
+extern "C" int calm_b200_seq_perf_stats(void* handle, int kind, char* name, int name_cap, double* ms_total, double* bytes_total, double* flops_total, long* launches) {
+	Seq& s = *(Seq*)handle;
+	if (kind < 0 || kind >= KD_COUNT) return 0;
+	snprintf(name, name_cap, "%s", kKindNames[kind]);
+	*ms_total = s.kind_ms[kind], *bytes_total = s.kind_bytes[kind], *flops_total = s.kind_flops[kind], *launches = s.kind_launches[kind];
+	return 1;
+}

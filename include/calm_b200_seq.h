@@ -1,0 +1,137 @@
+/*
+ * calm_b200_seq.h -- C ABI of libcalm_b200_seq.so: layer-list models served to MANY sequences at once.
+ *
+ * The calm boundary (calm_b200.h) serves one sequence of a Llama-shaped model per process.  This boundary serves models
+ * whose layers are given as a list (each entry names a token mixer and a feed-forward) to a batch of sequences, each with
+ * its own cache and recurrent state, and follows the same protocol: the host parses the container, uploads every tensor
+ * with calm_b200_seq_upload(), binds the device pointers in the records below and calls calm_b200_seq_prepare().  After
+ * that, sequences are opened, stepped (any number of new tokens per sequence and step: a prompt, a portion of one, or a
+ * single decoded token) and closed.  Errors that are the caller's (no slot, no page left, a closed slot) come back as
+ * negative return codes; CUDA failures print one line and abort(), as everywhere in this library.  No CPU fallback.
+ *
+ * Mixers (SeqLayer.type):
+ *   SEQ_LATENT  latent attention: queries and keys/values go through low-rank latents, only the normalised key/value
+ *               latent is cached; causal softmax; a sigmoid gate per head on the output.
+ *   SEQ_DELTA   gated delta rule with one decay per head and key channel: short causal convolutions + SiLU on q, k, v,
+ *               unit-norm q and k, a [dim x vdim] fp32 state per head carried from token to token.
+ *   SEQ_WINDOW  grouped-query attention behind short causal convolutions, unweighted RMS norm on q and k, a sliding
+ *               window of `window` positions and a learned per-head sink in the softmax denominator.
+ * Norms are Dynamic Tanh (tanh(alpha x) w + b), before and after each sublayer.  Feed-forward: clamped gated unit.
+ * A span of layers can be run several times in a row with the same weights (loop_*), each pass with its own state.
+ */
+#ifndef CALM_B200_SEQ_H
+#define CALM_B200_SEQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2 };
+
+/* a Dynamic Tanh norm: bf16 weight[n], bf16 bias[n], bf16 alpha[1] (device pointers) */
+struct SeqNorm {
+	const void* w;
+	const void* b;
+	const void* alpha;
+};
+
+/* One layer.  All matrices are bf16, row-major (out, in), device pointers.  w_in is the layer's input projections
+ * stacked by rows in the order given per mixer below. */
+struct SeqLayer {
+	int type;            /* enum SeqMixer */
+	int heads, kv_heads; /* SEQ_LATENT: kv_heads unused */
+	int dim, vdim;       /* per-head query/key width and value width */
+	int q_rank, kv_rank; /* SEQ_LATENT */
+	int taps;            /* SEQ_DELTA / SEQ_WINDOW: convolution taps (1 = none) */
+	int window;          /* SEQ_WINDOW: positions seen, the current one included; <= 0: unbounded */
+	int a_rank, g_rank;  /* SEQ_DELTA: inner widths of the decay and gate projections */
+	int ff;              /* feed-forward width, 0 = no feed-forward */
+	float scale;         /* score scale of the attentions */
+	float limit;         /* clamp of the feed-forward */
+	struct SeqNorm norm1, norm1b, norm2, norm2b;
+	/* SEQ_LATENT: rows [dq | dkv | g];  SEQ_DELTA: [q | k | v | b | a1 | g1];  SEQ_WINDOW: [q | k | v] */
+	const void* w_in;
+	const void* w_o;       /* (width, heads*vdim) */
+	/* SEQ_LATENT */
+	const void* dq_norm;   /* bf16 [q_rank] */
+	const void* dkv_norm;  /* bf16 [kv_rank] */
+	const void* w_uq;      /* (heads*dim, q_rank) */
+	const void* w_ukT;     /* per head the TRANSPOSED key up-projection: [heads][kv_rank][dim] */
+	const void* w_uv;      /* (heads*vdim, kv_rank) */
+	/* SEQ_DELTA / SEQ_WINDOW */
+	const void* conv;      /* bf16 [channels of q|k|v][taps] */
+	/* SEQ_DELTA */
+	const void* w_a2;      /* (heads*dim, a_rank) */
+	const void* w_g2;      /* (heads*vdim, g_rank) */
+	const void* a_log;     /* bf16 [heads] */
+	const void* dt_bias;   /* bf16 [heads*dim] */
+	const void* out_norm;  /* bf16 [vdim] */
+	/* SEQ_WINDOW */
+	const void* sink;      /* bf16 [heads] or NULL */
+	/* feed-forward */
+	const void* w_gate_up; /* rows [gate | up]: (2*ff, width) */
+	const void* w_down;    /* (width, ff) */
+};
+
+struct SeqModel {
+	int vocab, width, n_layers;
+	int loop_start, loop_stop, loop_times; /* layers [start, stop) run `times` times; times <= 1: no loop */
+	float eps;
+	int exact;       /* 1: every product in true fp32 (SIMT), 0: bf16 tensor-core products with fp32 accumulation */
+	int max_tokens;  /* tokens that live sequences hold at any time: sizes the paged cache */
+	int max_seqs;    /* sequence slots */
+	int page;        /* tokens per cache page */
+	const void* embed;  /* bf16 (vocab, width) */
+	const void* head;   /* bf16 (vocab, width) */
+	struct SeqNorm final_norm;
+	const struct SeqLayer* layers;
+};
+
+/* cudaMalloc + copy, like upload_cuda */
+void* calm_b200_seq_upload(const void* host, size_t size);
+void calm_b200_seq_free(void* device_ptr);
+
+/* Validate, allocate the page pool and per-slot state; returns an opaque handle (NULL never: failures abort). */
+void* calm_b200_seq_prepare(const struct SeqModel* model);
+void calm_b200_seq_release(void* handle);
+
+/* Sequence slots.  open: a free slot with empty cache and zero state, or -1.  close: pages and slot go back. */
+int calm_b200_seq_open(void* handle);
+int calm_b200_seq_close(void* handle, int slot);
+int calm_b200_seq_length(void* handle, int slot);
+int calm_b200_seq_free_pages(void* handle);
+
+/* One step over a batch: sequence i (slot slots[i]) is fed counts[i] new tokens, packed back to back in `tokens`.
+ * `want` lists n_want packed token indices (ascending or not) whose logits are computed; they stay on the device and,
+ * when logits_host != NULL, are copied there as float[n_want][vocab].  Returns 0, or -2 when the page pool is
+ * exhausted, -3 for a bad slot / count (nothing has run then). */
+int calm_b200_seq_step(void* handle, int n_seq, const int* slots, const int* counts, const int* tokens, int n_want, const int* want,
+                       float* logits_host);
+
+/* argmax (lowest index wins ties) of each row of the last step's logits -> out[n_want] */
+void calm_b200_seq_argmax(void* handle, int* out);
+/* device pointer of the last step's logits, float[n_want][vocab] */
+const float* calm_b200_seq_device_logits(void* handle);
+
+/* (tests) residual stream of the last step after layer run `run`: float[n_tokens][width]; only recorded when
+ * calm_b200_seq_set_trace(handle, 1) was called before the step */
+void calm_b200_seq_set_trace(void* handle, int on);
+int calm_b200_seq_layer_runs(void* handle);
+void calm_b200_seq_read_trace(void* handle, int run, float* out);
+
+uint64_t calm_b200_seq_launch_count(void);
+void calm_b200_seq_timer_start(void* handle);
+float calm_b200_seq_timer_stop(void* handle);
+/* per-kernel-kind device time of the steps since set_perf(handle, 1): events around every launch (slow; for the bench's
+ * roofline table only).  stats: returns 0 past the last kind. */
+void calm_b200_seq_set_perf(void* handle, int on);
+int calm_b200_seq_perf_stats(void* handle, int kind, char* name, int name_cap, double* ms_total, double* bytes_total, double* flops_total, long* launches);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CALM_B200_SEQ_H */
