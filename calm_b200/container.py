@@ -42,7 +42,7 @@ def write_tensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dict[st
     header, chunks, at = {}, [], 0
     for name, t in tensors.items():
         t = t.contiguous()
-        b = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        b = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(b)]}
         chunks.append(b)
         at += len(b)

@@ -1,0 +1,156 @@
+"""Throughput of the Vimulorn family at layer sizes of real models (random weights), beside the calm engine's closest
+model -- a Llama-shaped stack of the same width, depth, head geometry and feed-forward width in fp16 -- on the same GPU.
+
+Per size: prompt throughput (one prompt of `prompt` tokens as one step), decode throughput for one sequence and for a
+batch, each after warm-up, timed with CUDA events on the library's stream; then one profiled pass that brackets every
+launch with events and reports, per kind of kernel, its time and its distance from the roofline (bytes / measured copy
+bandwidth, flops / measured bf16 GEMM throughput, whichever is larger).  Inputs exceed L2 at every size (weights alone
+are hundreds of MB), so no flush between iterations."""
+from __future__ import annotations
+
+import json
+import os
+import time
+from dataclasses import replace
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SIZES = {
+    # name: (width, ff, blocks of [latent, delta, window], heads, head dim, kv heads, kv_rank, q_rank, window, vocab)
+    "w1024": dict(width=1024, ff=2816, blocks=2, heads=8, dim=128, kv_heads=2, kv_rank=256, q_rank=384, window=512, vocab=32000),
+    "w2048": dict(width=2048, ff=5632, blocks=2, heads=16, dim=128, kv_heads=4, kv_rank=512, q_rank=768, window=1024, vocab=32000),
+    "w4096": dict(width=4096, ff=11264, blocks=1, heads=32, dim=128, kv_heads=8, kv_rank=512, q_rank=1536, window=1024, vocab=32000),
+}
+
+
+def vimulorn_config(z: dict) -> dict:
+    mlp = {"ff": z["ff"], "kind": "dense", "limit": 7.0}
+    H, D = z["heads"], z["dim"]
+    block = [
+        {"type": "latent_attention", "mixer": {"heads": H, "dim": D, "vdim": D, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"], "scale": D ** -0.5}, "mlp": mlp},
+        {"type": "channel_delta", "mixer": {"heads": H, "kv_heads": H, "dim": D, "vdim": D, "conv": 4, "a_rank": 64, "g_rank": 64}, "mlp": mlp},
+        {"type": "attention", "mixer": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": D, "conv": 4, "mask": {"size": z["window"]}, "scale": D ** -0.5}, "mlp": mlp},
+    ]
+    return {"architecture": "Vimulorn", "layers": block * z["blocks"], "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def roofline_table(stats: dict, hbm_gbs: float, tflops: float) -> dict:
+    out = {}
+    for k, (ms, by, fl, n) in stats.items():
+        if not n or ms <= 0:
+            continue
+        floor_ms = max(by / (hbm_gbs * 1e9), fl / (tflops * 1e12)) * 1e3
+        out[k] = {"ms": round(ms, 4), "launches": n, "gbs": round(by / 1e9 / (ms / 1e3), 1), "tflops": round(fl / 1e12 / (ms / 1e3), 2),
+                  "bound": "hbm" if by / (hbm_gbs * 1e9) >= fl / (tflops * 1e12) else "tensor", "frac_of_roofline": round(floor_ms / ms, 4)}
+    return out
+
+
+def bench_vimulorn(name: str, prompt: int, batch: int, steps: int, warmup: int, seed: int = 0) -> list:
+    from . import vimulorn
+
+    z = SIZES[name]
+    cfg = vimulorn_config(z)
+    hbm, tf, src = peaks()
+    t0 = time.time()
+    tensors = vimulorn.random_tensors(cfg, seed)
+    params = sum(t.numel() for t in tensors.values())
+    rng = np.random.default_rng(seed)
+    lines = []
+    with vimulorn.from_tensors(cfg, tensors, "bfloat16", max_tokens=(batch + 1) * (prompt + steps + warmup + 8), max_seqs=batch + 1, page=16) as m:
+        del tensors
+        toks = [int(x) for x in rng.integers(0, z["vocab"], prompt)]
+
+        def prefill_once(profile=False):
+            s = m.open()
+            m.timer_start()
+            m.step([s], [toks], [prompt - 1], fetch=False)
+            ms = m.timer_stop()
+            m.close_seq(s)
+            return ms
+
+        for _ in range(max(warmup // 4, 3)):
+            prefill_once()
+        ms = min(prefill_once() for _ in range(5))
+        m.perf(True)
+        prefill_once()
+        table = roofline_table(m.perf_stats(), hbm, tf)
+        m.perf(False)
+        lines.append({"family": "vimulorn", "size": name, "phase": "prefill", "tokens": prompt, "ms": round(ms, 3), "tokens_per_s": round(prompt / ms * 1e3, 1),
+                      "params": params, "kernels": table, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}})
+        for b in sorted({1, batch}):
+            slots = [m.open() for _ in range(b)]
+            m.step(slots, [toks] * b, [], fetch=False)
+            nxt = [[int(rng.integers(0, z["vocab"]))] for _ in range(b)]
+            for _ in range(warmup):
+                m.step(slots, nxt, list(range(b)), fetch=False)
+            m.timer_start()
+            for _ in range(steps):
+                m.step(slots, nxt, list(range(b)), fetch=False)
+            ms = m.timer_stop() / steps
+            m.perf(True)
+            m.step(slots, nxt, list(range(b)), fetch=False)
+            table = roofline_table(m.perf_stats(), hbm, tf)
+            m.perf(False)
+            for s in slots:
+                m.close_seq(s)
+            lines.append({"family": "vimulorn", "size": name, "phase": "decode", "batch": b, "context": prompt, "ms_per_step": round(ms, 4),
+                          "tokens_per_s": round(b / ms * 1e3, 1), "kernels": table})
+    for ln in lines:
+        ln["setup_s"] = round(time.time() - t0, 1)
+    return lines
+
+
+def bench_llama_twin(name: str, prompt: int, steps: int, warmup: int, seed: int = 0) -> list:
+    """The calm engine on a Llama-shaped model of the same width / depth / heads / feed-forward, fp16 weights."""
+    from . import lib
+    from . import modelgen as mg
+
+    z = SIZES[name]
+    spec = mg.ModelSpec("twin-" + name, z["width"], z["ff"], 3 * z["blocks"], z["heads"], z["kv_heads"], z["dim"], z["vocab"], "fp16", max_seq_len=prompt + steps + warmup + 64)
+    host = mg.HostModel(spec, seed=seed)
+    toks = mg.teacher_tokens(spec.vocab_size, prompt)
+    L = lib.load()
+    lines = []
+    with lib.DeviceModel(spec, host.tensors, seq_len=spec.max_seq_len) as dm:
+        best, served = 1e30, 0
+        for i in range(5):
+            L.calm_b200_timer_start()
+            served = dm.prefill(toks, 0)
+            best = min(best, L.calm_b200_timer_stop()) if i >= 2 else best
+        lines.append({"family": "llama-twin", "size": name, "phase": "prefill", "tokens": prompt, "ms": round(best, 3), "tokens_per_s": round(prompt / best * 1e3, 1),
+                      "tensor_core_pass": bool(served)})
+        dm.decode_greedy(1, prompt, warmup)
+        L.calm_b200_timer_start()
+        dm.decode_greedy(1, prompt + warmup, steps)
+        ms = L.calm_b200_timer_stop() / steps
+        stats, span = dm.profile(23, prompt + warmup + steps, 8)
+        hbm = peaks()[0]
+        table = {k: {"us_per_launch": round(v[0] / max(v[2], 1) * 1e3, 2), "frac_of_roofline": round(v[1] / 1e9 / (v[0] / 1e3) / hbm, 4)} for k, v in stats.items() if v[2] and v[0] > 0}
+        lines.append({"family": "llama-twin", "size": name, "phase": "decode", "batch": 1, "context": prompt, "ms_per_step": round(ms, 4), "tokens_per_s": round(1e3 / ms, 1),
+                      "kernels": table})
+    return lines
+
+
+def main(sizes, prompt=2048, batch=16, steps=32, warmup=8, twin=True):
+    from . import build as cbuild
+
+    cbuild.build(target="seq")
+    if twin:
+        cbuild.build(target="engine")
+    os.environ.setdefault("CALM_B200_QUIET", "1")
+    out = []
+    for name in sizes:
+        for ln in bench_vimulorn(name, prompt, batch, steps, warmup) + (bench_llama_twin(name, prompt, steps, warmup) if twin else []):
+            print(json.dumps(ln), flush=True)
+            out.append(ln)
+    return out

@@ -1,0 +1,240 @@
+"""The Vimulorn family on the layer-list runtime against the plain float64 statement in vimulorn_plain.py.
+
+Every test makes its own small configuration and seeded weights.  float32 mode is compared tightly (it shows any wrong
+key, window edge, lost state or missing sink); bfloat16 mode within bf16 rounding.  Where random weights would hide a
+fault the weights are sharpened (queries and keys scaled up so single keys dominate the softmax, large sinks)."""
+import copy
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import vimulorn_plain as plain  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+from calm_b200 import serving, vimulorn  # noqa: E402
+
+MLP = {"ff": 40, "kind": "dense", "limit": 1.5}
+
+
+def latent(heads=4, dim=16, vdim=24, kv_rank=40, q_rank=24, scale=0.3, mlp=MLP):
+    return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale}, "mlp": mlp}
+
+
+def delta(heads=4, kv_heads=2, dim=16, vdim=24, conv=4, a_rank=8, g_rank=12, mlp=MLP):
+    return {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "a_rank": a_rank, "g_rank": g_rank}, "mlp": mlp}
+
+
+def window(heads=6, kv_heads=2, dim=16, vdim=20, conv=2, size=7, scale=0.4, mlp=MLP):
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "mask": {"size": size}, "scale": scale}, "mlp": mlp}
+
+
+def config(layers, width=48, vocab=97, loop=None, eps=1e-5):
+    cfg = {"architecture": "Vimulorn", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def weights(cfg, seed=0, sharpen=0.0, sink=None):
+    t = vimulorn.random_tensors(cfg, seed)
+    for name in list(t):
+        if sharpen and name.endswith((".mix.uq", ".mix.q")) and ".conv" not in name:
+            t[name] = (t[name].float() * sharpen).to(torch.bfloat16)
+        if sink is not None and name.endswith(".sink"):
+            t[name] = torch.full_like(t[name], sink)
+    return t
+
+
+def as_f64(t):
+    return {k: v.float().numpy().astype(np.float64) for k, v in t.items()}
+
+
+def tokens(cfg, n, seed=1):
+    return [int(x) for x in np.random.default_rng(seed).integers(0, cfg["vocab"], n)]
+
+
+def rel_err(got, ref):
+    d = got - ref
+    d = d - d.mean(-1, keepdims=True)
+    r = ref - ref.mean(-1, keepdims=True)
+    return float(np.sqrt((d * d).mean(-1)).max() / np.sqrt((r * r).mean()))
+
+
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+def whole(model, toks):
+    s = model.open()
+    out = model.step([s], [toks], list(range(len(toks))))
+    model.close_seq(s)
+    return out
+
+
+def check_all_ways(cfg, t, toks, dtype="float32", portions=(5, 2, 1), page=4):
+    """whole prompt, prompt + token-by-token decoding, and portions: all against the plain statement."""
+    ref = plain.forward(cfg, as_f64(t), toks)
+    with vimulorn.from_tensors(cfg, t, dtype, max_tokens=4 * len(toks) + 64, max_seqs=4, page=page) as m:
+        got = whole(m, toks)
+        assert rel_err(got, ref) < TOL[dtype]
+        for first in {1, max(1, len(toks) // 2)}:
+            s = m.open()
+            rows = [m.step([s], [toks[:first]], list(range(first)))]
+            for p in range(first, len(toks)):
+                rows.append(m.step([s], [[toks[p]]], [0]))
+            m.close_seq(s)
+            assert rel_err(np.concatenate(rows), ref) < TOL[dtype]
+        for size in portions:
+            s, rows, at = m.open(), [], 0
+            while at < len(toks):
+                part = toks[at:at + size]
+                rows.append(m.step([s], [part], list(range(len(part)))))
+                at += len(part)
+                size = size + 1 if size > 2 else size  # growing portions: edges fall at ever different places
+            m.close_seq(s)
+            assert rel_err(np.concatenate(rows), ref) < TOL[dtype]
+    return ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [latent(), delta(), window(), latent(mlp=None), delta(heads=3, kv_heads=3, dim=24, vdim=8, conv=1, mlp=None), window(heads=2, kv_heads=2, size=1)],
+                         ids=["latent", "delta", "window", "latent-noff", "delta-taps1", "window-size1"])
+def test_each_mixer_alone(layer, dtype):
+    cfg = config([layer])
+    check_all_ways(cfg, weights(cfg, 3), tokens(cfg, 37), dtype)
+
+
+def test_mixed_stack_with_loop_in_the_middle():
+    cfg = config([window(conv=3, size=5), latent(), delta(), window(heads=4, kv_heads=4, dim=8, vdim=8, conv=4, size=9)], width=40, loop=(1, 3, 2))
+    assert plain.layer_runs(cfg)[0] == [0, 1, 2, 1, 2, 3]
+    check_all_ways(cfg, weights(cfg, 5), tokens(cfg, 41))
+
+
+def test_residual_stream_after_every_run():
+    cfg = config([latent(), delta(), window()], loop=(0, 2, 3))
+    t, toks = weights(cfg, 8), tokens(cfg, 19)
+    trace = []
+    plain.forward(cfg, as_f64(t), toks, trace)
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=64, max_seqs=2) as m:
+        m.set_trace(True)
+        whole(m, toks)
+        got = m.read_trace(len(toks))
+    assert got.shape[0] == len(trace) == 7
+    for g, r in zip(got, trace):
+        assert np.abs(g - r).max() < 1e-4 * max(1.0, np.abs(r).max())
+
+
+def test_window_edges_show():
+    """Sharp scores and a large window-relative length: a window one token too wide or too narrow moves the logits far more
+    than the tolerance, in prompts and in decoding alike."""
+    cfg = config([window(size=6, conv=2, scale=1.0)])
+    t = weights(cfg, 11, sharpen=6.0)
+    toks = tokens(cfg, 60)
+    ref = check_all_ways(cfg, t, toks, portions=(7, 2))
+    for off in (-1, 1):
+        wrong = copy.deepcopy(cfg)
+        wrong["layers"][0]["mixer"]["mask"]["size"] += off
+        assert rel_err(plain.forward(wrong, as_f64(t), toks), ref) > 100 * TOL["float32"]
+
+
+def test_sink_shows():
+    cfg = config([window(size=8)])
+    t = weights(cfg, 12, sink=3.0)
+    toks = tokens(cfg, 30)
+    ref = check_all_ways(cfg, t, toks)
+    none = {k: (torch.full_like(v, -60.0) if k.endswith(".sink") else v) for k, v in t.items()}
+    assert rel_err(plain.forward(cfg, as_f64(none), toks), ref) > 100 * TOL["float32"]
+
+
+def test_far_keys_and_page_borders():
+    """Peaked latent attention over a prompt of many pages: single far keys carry the output."""
+    cfg = config([latent(scale=1.0), window(size=33, scale=1.0)])
+    t = weights(cfg, 13, sharpen=5.0)
+    toks = tokens(cfg, 150)
+    ref = plain.forward(cfg, as_f64(t), toks)
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=400, max_seqs=2, page=16) as m:
+        assert rel_err(whole(m, toks), ref) < TOL["float32"]
+        s = m.open()
+        rows = [m.step([s], [toks[:100]], list(range(100)))]
+        for p in range(100, 150):  # decoding across the borders of pages 6..9 and with the window's far edge moving through them
+            rows.append(m.step([s], [[toks[p]]], [0]))
+        assert rel_err(np.concatenate(rows), ref) < TOL["float32"]
+
+
+def test_long_decoding_keeps_state():
+    cfg = config([delta(conv=3), window(size=12, conv=3)])
+    t, toks = weights(cfg, 14), tokens(cfg, 130)
+    ref = plain.forward(cfg, as_f64(t), toks)
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=200, max_seqs=2, page=8) as m:
+        s = m.open()
+        rows = [m.step([s], [[x]], [0]) for x in toks]
+        assert rel_err(np.concatenate(rows), ref) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_batch_equals_each_alone(dtype):
+    cfg = config([latent(), delta(), window()], loop=(0, 2, 2))
+    t = weights(cfg, 21)
+    prompts = [tokens(cfg, n, seed=n) for n in (1, 9, 30, 2)]
+    tails = [tokens(cfg, n, seed=50 + n) for n in (6, 3, 0, 6)]
+    p = as_f64(t)
+    refs = [plain.forward(cfg, p, a + b) for a, b in zip(prompts, tails)]
+    with vimulorn.from_tensors(cfg, t, dtype, max_tokens=192, max_seqs=5, page=4) as m:
+        slots = [m.open() for _ in prompts]
+        want = list(range(sum(len(a) for a in prompts)))
+        out = m.step(slots, prompts, want)
+        got, at = [], 0
+        for a in prompts:
+            got.append([out[at:at + len(a)]])
+            at += len(a)
+        for k in range(6):  # decoded together; the shorter ones leave earlier
+            live = [i for i, b in enumerate(tails) if k < len(b)]
+            o = m.step([slots[i] for i in live], [[tails[i][k]] for i in live], list(range(len(live))))
+            for j, i in enumerate(live):
+                got[i].append(o[j:j + 1])
+        for i, r in enumerate(refs):
+            assert rel_err(np.concatenate(got[i]), r) < TOL[dtype]
+        if dtype == "float32":  # a row does not depend on what else is in the batch: bit for bit
+            alone = whole(m, prompts[2])
+            assert np.array_equal(alone, np.concatenate(got[2])[:30])
+
+
+def test_slots_and_pages_are_used_again():
+    cfg = config([latent(), delta(), window()])
+    t = weights(cfg, 22)
+    p = as_f64(t)
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=48, max_seqs=2, page=4) as m:
+        free0 = m.free_pages()
+        for rnd in range(4):  # every round fills the pool almost completely, with other lengths than the round before
+            a, b = tokens(cfg, 20 + rnd, seed=rnd), tokens(cfg, 23 - rnd, seed=9 + rnd)
+            sa, sb = m.open(), m.open()
+            out = m.step([sa, sb], [a, b], list(range(len(a) + len(b))))
+            assert rel_err(out[:len(a)], plain.forward(cfg, p, a)) < TOL["float32"]
+            assert rel_err(out[len(a):], plain.forward(cfg, p, b)) < TOL["float32"]
+            m.close_seq(sb if rnd % 2 else sa)
+            m.close_seq(sa if rnd % 2 else sb)
+            assert m.free_pages() == free0
+        s = m.open()
+        with pytest.raises(Exception):
+            m.step([s], [tokens(cfg, 4 * free0 + 1)], [0])  # more than the pool holds: refused, nothing has run
+        assert m.length(s) == 0
+
+
+def test_greedy_generation_through_the_scheduler():
+    cfg = config([latent(), delta(), window()], loop=(1, 2, 2))
+    t = weights(cfg, 23)
+    p = as_f64(t)
+    prompts = [tokens(cfg, n, seed=70 + n) for n in (5, 17, 1)]
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=256, max_seqs=2, page=8) as m:
+        outs = serving.generate(m, prompts, 12, max_batch=2)  # three requests, two slots: a second batch follows the first
+        assert m.free_pages() == 256 // 8 + 2
+    for pr, out in zip(prompts, outs):
+        assert len(out) == 12
+        lg = plain.forward(cfg, p, pr + out)
+        for k, tok in enumerate(out):  # each generated token is the plain statement's argmax given the same history
+            row = lg[len(pr) + k - 1]
+            assert tok == int(row.argmax()) or row.max() - row[tok] < 1e-4 * np.abs(row).max()
