@@ -192,7 +192,8 @@ __global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int t
 // the output through a sigmoid.
 #define ATT_KC 64
 #define ATT_THREADS 256
-#define ATT_MAXI 32 // output elements per thread
+#define ATT_MAXI 32 // output elements per thread: heads of the tile x value columns per thread
+#define ATT_KPL 16  // key channels per lane held in registers (keys up to 512 wide)
 struct AttArgs {
 	const float* q;   // [N][heads][kd]
 	const float* kc;  // cache rows of width kld
@@ -206,14 +207,18 @@ struct AttArgs {
 	const bf16* sink; // [heads] or null
 	const float* gate;
 	int ldg;          // gate[n * ldg + h]
+	const int* skip;  // [N] or null: 1 = this token's attention is computed by the product path (k_seq_attn_*), the CTA leaves
+	int nsplit;       // CTAs that share one (token, head tile)'s keys; > 1: partial results go to `part`, k_seq_attention_merge finishes
+	float* part;      // [N][heads][nsplit][vd + 2]: unnormalised output, running maximum, denominator
 };
 template <typename AT>
 __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* out, SeqBatch sb) {
 	extern __shared__ float sm[];
 	const int n = blockIdx.x, h0 = blockIdx.y * a.tile, R = a.tile;
+	if (a.skip && a.skip[n]) return;
 	const int kvh = h0 / a.group;
 	float* qs = sm;                  // [R][kd]
-	float* sc = qs + R * a.kd;       // [R][ATT_KC]
+	float* sc = qs + ((R * a.kd + 3) & ~3); // [R][ATT_KC], 16-byte aligned
 	float* mrow = sc + R * ATT_KC;   // [R] running maximum
 	float* lrow = mrow + R;          // [R] running denominator
 	float* frow = lrow + R;          // [R] rescale factor of this chunk
@@ -221,29 +226,46 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = ATT_THREADS / 32;
 	const int slot = sb.tslot[n], pos = sb.tpos[n];
 	const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+	// this CTA's share of the key chunks (the whole range when nsplit == 1)
+	const int nchunk = (pos - lo) / ATT_KC + 1, per = (nchunk + a.nsplit - 1) / a.nsplit;
+	const int c_begin = lo + (int)blockIdx.z * per * ATT_KC, c_end = min(pos, lo + ((int)blockIdx.z + 1) * per * ATT_KC - 1);
 	for (int i = tid; i < R * a.kd; i += ATT_THREADS) qs[i] = a.q[((size_t)n * a.heads + h0) * a.kd + i];
 	if (tid < R) {
-		const float s = a.sink ? ldf(a.sink + h0 + tid) : -INFINITY;
-		mrow[tid] = s, lrow[tid] = a.sink ? 1.f : 0.f;
+		const bool sk = a.sink && blockIdx.z == 0; // the sink counts once: in the first share
+		mrow[tid] = sk ? ldf(a.sink + h0 + tid) : -INFINITY, lrow[tid] = sk ? 1.f : 0.f;
 	}
 	float acc[ATT_MAXI];
 #pragma unroll
 	for (int i = 0; i < ATT_MAXI; ++i) acc[i] = 0.f;
-	const int items = R * a.vd;
+	const bool wide = a.vd > 2 * ATT_THREADS;
 	__syncthreads();
-	for (int c0 = lo; c0 <= pos; c0 += ATT_KC) {
+	for (int c0 = c_begin; c0 <= c_end; c0 += ATT_KC) {
 		const int nk = min(ATT_KC, pos - c0 + 1);
 		if (tid < ATT_KC) rows[tid] = tid < nk ? cache_row(sb, slot, c0 + tid) : 0;
 		__syncthreads();
-		// scores: one warp per key, lanes across the key's channels
+		// scores: one warp per key, lanes across the key's channels; the lane's slice of the key is read once for all heads
 		for (int j = warp; j < ATT_KC; j += nwarp) {
 			if (j < nk) {
 				const float* kr = a.kc + rows[j] * a.kld + (size_t)kvh * a.kd;
-				for (int r = 0; r < R; ++r) {
-					float d = 0.f;
-					for (int i = lane; i < a.kd; i += 32) d += qs[r * a.kd + i] * kr[i];
-					d = warp_sum(d);
-					if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+				if (a.kd <= 32 * ATT_KPL) {
+					float kv[ATT_KPL];
+#pragma unroll
+					for (int i = 0; i < ATT_KPL; ++i) kv[i] = i * 32 + lane < a.kd ? kr[i * 32 + lane] : 0.f;
+					for (int r = 0; r < R; ++r) {
+						float d = 0.f;
+#pragma unroll
+						for (int i = 0; i < ATT_KPL; ++i)
+							if (i * 32 < a.kd) d = fmaf(qs[r * a.kd + min(i * 32 + lane, a.kd - 1)], kv[i], d);
+						d = warp_sum(d);
+						if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+					}
+				} else {
+					for (int r = 0; r < R; ++r) {
+						float d = 0.f;
+						for (int i = lane; i < a.kd; i += 32) d += qs[r * a.kd + i] * kr[i];
+						d = warp_sum(d);
+						if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+					}
 				}
 			} else if (lane == 0) {
 				for (int r = 0; r < R; ++r) sc[r * ATT_KC + j] = -INFINITY;
@@ -268,29 +290,175 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 			}
 		}
 		__syncthreads();
-		// values
+		// values: a thread owns value columns tid and tid + 256 for every head of the tile (accumulator c * 16 + r); values wider
+		// than 512 run one head per CTA with up to 32 columns per thread (accumulator c)
+		if (wide) {
 #pragma unroll
-		for (int k = 0; k < ATT_MAXI; ++k) {
-			const int it = tid + k * ATT_THREADS;
-			if (it < items) {
-				const int r = it / a.vd, d = it % a.vd;
-				float s = acc[k] * frow[r];
-				for (int j = 0; j < nk; ++j) s += sc[r * ATT_KC + j] * a.vc[rows[j] * a.vld + (size_t)kvh * a.vd + d];
-				acc[k] = s;
+			for (int k = 0; k < ATT_MAXI; ++k) {
+				const int d = tid + k * ATT_THREADS;
+				if (d < a.vd) {
+					const float* vcol = a.vc + (size_t)kvh * a.vd + d;
+					float s = acc[k] * frow[0];
+					for (int j = 0; j < nk; ++j) s = fmaf(sc[j], vcol[rows[j] * a.vld], s);
+					acc[k] = s;
+				}
+			}
+		} else {
+#pragma unroll
+			for (int c = 0; c < 2; ++c) {
+				const int d = tid + c * ATT_THREADS;
+				if (d < a.vd) {
+					const float* vcol = a.vc + (size_t)kvh * a.vd + d;
+#pragma unroll
+					for (int r = 0; r < 16; ++r)
+						if (r < R) acc[c * 16 + r] *= frow[r];
+					for (int j0 = 0; j0 < nk; j0 += 4) {
+						float v[4];
+#pragma unroll
+						for (int u = 0; u < 4; ++u) v[u] = j0 + u < nk ? vcol[rows[j0 + u] * a.vld] : 0.f;
+#pragma unroll
+						for (int r = 0; r < 16; ++r) {
+							if (r < R) {
+								const float4 p = *(const float4*)(sc + r * ATT_KC + j0);
+								acc[c * 16 + r] = fmaf(p.w, v[3], fmaf(p.z, v[2], fmaf(p.y, v[1], fmaf(p.x, v[0], acc[c * 16 + r]))));
+							}
+						}
+					}
+				}
 			}
 		}
 		__syncthreads();
 	}
+	// accumulator k -> (head of the tile, value column)
+	auto head_of = [&](int k) { return wide ? 0 : k % 16; };
+	auto col_of = [&](int k) { return tid + (wide ? k : k / 16) * ATT_THREADS; };
+	if (a.nsplit > 1) {
+		const int pw = a.vd + 2;
+#pragma unroll
+		for (int k = 0; k < ATT_MAXI; ++k) {
+			const int r = head_of(k), d = col_of(k);
+			if (r < R && d < a.vd) a.part[(((size_t)n * a.heads + h0 + r) * a.nsplit + blockIdx.z) * pw + d] = acc[k];
+		}
+		if (tid < R) {
+			float* p = a.part + (((size_t)n * a.heads + h0 + tid) * a.nsplit + blockIdx.z) * pw + a.vd;
+			p[0] = mrow[tid], p[1] = lrow[tid];
+		}
+		return;
+	}
 #pragma unroll
 	for (int k = 0; k < ATT_MAXI; ++k) {
-		const int it = tid + k * ATT_THREADS;
-		if (it < items) {
-			const int r = it / a.vd, d = it % a.vd;
+		const int r = head_of(k), d = col_of(k);
+		if (r < R && d < a.vd) {
 			float v = acc[k] / lrow[r];
 			if (a.gate) v *= sigmoidf_(a.gate[(size_t)n * a.ldg + h0 + r]);
 			out[((size_t)n * a.heads + h0 + r) * a.vd + d] = to_act<AT>(v);
 		}
 	}
+}
+// folds the shares of one (token, head) in share order: one CTA per (token, head)
+template <typename AT>
+__global__ void k_seq_attention_merge(AttArgs a, AT* out) {
+	const int n = blockIdx.x, h = blockIdx.y, pw = a.vd + 2;
+	if (a.skip && a.skip[n]) return;
+	const float* p = a.part + ((size_t)n * a.heads + h) * a.nsplit * pw;
+	float mx = -INFINITY;
+	for (int z = 0; z < a.nsplit; ++z) mx = fmaxf(mx, p[z * pw + a.vd]);
+	float l = 0.f;
+	for (int z = 0; z < a.nsplit; ++z) {
+		const float m = p[z * pw + a.vd];
+		if (m != -INFINITY) l += p[z * pw + a.vd + 1] * expf(m - mx);
+	}
+	const float g = (a.gate ? sigmoidf_(a.gate[(size_t)n * a.ldg + h]) : 1.f) / l;
+	for (int d = threadIdx.x; d < a.vd; d += blockDim.x) {
+		float v = 0.f;
+		for (int z = 0; z < a.nsplit; ++z) {
+			const float m = p[z * pw + a.vd];
+			if (m != -INFINITY) v += p[z * pw + d] * expf(m - mx);
+		}
+		out[((size_t)n * a.heads + h) * a.vd + d] = to_act<AT>(v * g);
+	}
+}
+
+// ---------------------------------------------------------------- prompt attention as products
+// For many query tokens of one sequence the scores and the weighted values are matrix products on the tensor cores:
+// the keys of the visible range are gathered from the paged cache into a bf16 matrix (values transposed), S = Q K^T per
+// head, a row-wise fp32 softmax applies scale, causal / window mask, sink and output gate and writes bf16 probabilities,
+// then O = P V.  k_seq_attention above serves single decoded tokens, short portions and the exact mode.
+struct AttGather {
+	const float* kc;
+	const float* vc;
+	int kld, vld, kcol, vcol; // column of this key/value head inside a cache row
+	int kd, vd;
+	bf16* Kb;   // [C][kd]
+	bf16* Vt;   // [vd][Cp]
+	int slot, k0, C, Cp;
+};
+__global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
+	__shared__ float tile[32][33];
+	const int j0 = blockIdx.x * 32, tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8 threads
+	const int dmax = max(a.kd, a.vd);
+	for (int d0 = blockIdx.y * 32; d0 < dmax; d0 += gridDim.y * 32) {
+		for (int r = ty; r < 32; r += 8) {
+			const int j = j0 + r, d = d0 + tx;
+			if (j < a.C) {
+				const long row = cache_row(sb, a.slot, a.k0 + j);
+				if (d < a.kd) a.Kb[(size_t)j * a.kd + d] = __float2bfloat16_rn(a.kc[row * a.kld + a.kcol + d]);
+				tile[r][tx] = d < a.vd ? a.vc[row * a.vld + a.vcol + d] : 0.f;
+			} else tile[r][tx] = 0.f;
+		}
+		__syncthreads();
+		for (int r = ty; r < 32; r += 8) {
+			const int d = d0 + r, j = j0 + tx;
+			if (d < a.vd && j < a.Cp) a.Vt[(size_t)d * a.Cp + j] = __float2bfloat16_rn(tile[tx][r]);
+		}
+		__syncthreads();
+	}
+}
+struct AttSoftmax {
+	const float* S; // [heads of the launch][T][Cp]
+	bf16* P;        // same shape
+	int T, C, Cp;
+	int qpos0, k0, window;
+	float scale;
+	const bf16* sink; // already offset to the first head of the launch, or null
+	const float* gate; // gate[t * ldg + z], already offset to the first token and head, or null
+	int ldg;
+};
+__global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
+	__shared__ float red[8];
+	__shared__ float bc;
+	const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x;
+	const float* srow = a.S + ((size_t)z * a.T + t) * a.Cp;
+	bf16* prow = a.P + ((size_t)z * a.T + t) * a.Cp;
+	const int qpos = a.qpos0 + t;
+	const int hi = min(a.C - 1, qpos - a.k0);                                  // last visible column
+	const int lo = a.window > 0 ? max(0, qpos - a.window + 1 - a.k0) : 0;      // first visible column
+	const float sk = a.sink ? ldf(a.sink + z) : -INFINITY;
+	float mx = sk;
+	for (int j = lo + tid; j <= hi; j += 256) mx = fmaxf(mx, srow[j] * a.scale);
+	mx = warp_max(mx);
+	if ((tid & 31) == 0) red[tid >> 5] = mx;
+	__syncthreads();
+	if (tid == 0) {
+		for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+		bc = mx;
+	}
+	__syncthreads();
+	mx = bc;
+	float sum = 0.f;
+	for (int j = lo + tid; j <= hi; j += 256) sum += expf(srow[j] * a.scale - mx);
+	sum = warp_sum(sum);
+	__syncthreads();
+	if ((tid & 31) == 0) red[tid >> 5] = sum;
+	__syncthreads();
+	if (tid == 0) {
+		for (int w = 1; w < 8; ++w) sum += red[w];
+		if (a.sink) sum += expf(sk - mx);
+		bc = (a.gate ? sigmoidf_(a.gate[(size_t)t * a.ldg + z]) : 1.f) / sum;
+	}
+	__syncthreads();
+	const float f = bc;
+	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi ? expf(srow[j] * a.scale - mx) * f : 0.f);
 }
 
 // ---------------------------------------------------------------- gated delta rule
@@ -349,6 +517,84 @@ __global__ void k_seq_delta_scan(DeltaArgs a, SeqBatch sb) {
 	}
 	__syncthreads();
 	for (int i = tid; i < D * V; i += blockDim.x) Sg[i] = S[i];
+}
+// The same recurrence with the state in registers: four lanes share a value column, each holding D/4 of its rows; the
+// next token's k, q, decay, v and beta are staged into the other half of a double buffer while the current token is
+// applied (one barrier per token).
+template <int D>
+__global__ void __launch_bounds__(512) k_seq_delta_scan_reg(DeltaArgs a, SeqBatch sb) {
+	constexpr int Q = D / 4, QP = Q + 1; // padded quarter: the four lanes of a column read different banks
+	extern __shared__ float sm[];
+	const int b = blockIdx.x, h = blockIdx.y, V = a.vdim;
+	const int kh = h / (a.heads / a.kv_heads);
+	const int tid = threadIdx.x, part = tid & 3;
+	const bool live = (tid >> 2) < V;          // lanes past the last column run along on a copy of it (whole warps shuffle)
+	const int col = live ? tid >> 2 : V - 1;
+	const int stage_len = 3 * 4 * QP + V + 1; // k, q, g (padded quarters), v, beta
+	float* buf[2] = {sm, sm + stage_len};
+	float S[Q];
+	float* Sg = a.state + ((size_t)sb.sslot[b] * a.heads + h) * D * V;
+#pragma unroll
+	for (int i = 0; i < Q; ++i) S[i] = Sg[(size_t)(part * Q + i) * V + col];
+	const float A = expf(ldf(a.a_log + h));
+	const int start = sb.sstart[b], cnt = sb.scount[b];
+	// item `it` of a token's stage: [0, D) k, [D, 2D) q, [2D, 3D) decay, [3D, 3D + V) v, 3D + V beta
+	auto fetch = [&](int n, int it) -> float {
+		if (it < D) return a.k[((size_t)n * a.kv_heads + kh) * D + it];
+		if (it < 2 * D) return a.q[((size_t)n * a.kv_heads + kh) * D + it - D];
+		if (it < 3 * D) return expf(-A * softplusf_(a.dt[((size_t)n * a.heads + h) * D + it - 2 * D] + ldf(a.dt_bias + h * D + it - 2 * D)));
+		if (it < 3 * D + V) return a.v[((size_t)n * a.heads + h) * V + it - 3 * D];
+		return sigmoidf_(a.proj[(size_t)n * a.ldp + a.bcol + h]);
+	};
+	auto put = [&](float* st, int it, float v) {
+		if (it < 3 * D) st[(it / D) * 4 * QP + ((it % D) / Q) * QP + (it % D) % Q] = v;
+		else st[3 * 4 * QP + it - 3 * D] = v;
+	};
+	const int items = 3 * D + V + 1;
+	for (int it = tid; it < items; it += blockDim.x) put(buf[0], it, fetch(start, it));
+	__syncthreads();
+	for (int t = 0; t < cnt; ++t) {
+		const int n = start + t;
+		float* cur = buf[t & 1];
+		float* nxt = buf[(t + 1) & 1];
+		float pre[2];
+		const bool more = t + 1 < cnt;
+		if (more) {
+#pragma unroll
+			for (int r = 0; r < 2; ++r) pre[r] = tid + r * (int)blockDim.x < items ? fetch(n + 1, tid + r * blockDim.x) : 0.f;
+		}
+		{
+			const float *ks = cur + part * QP, *qs = cur + 4 * QP + part * QP, *gs = cur + 8 * QP + part * QP;
+			float dot = 0.f;
+#pragma unroll
+			for (int i = 0; i < Q; ++i) {
+				S[i] *= gs[i];
+				dot = fmaf(S[i], ks[i], dot);
+			}
+			dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+			dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+			const float u = cur[3 * 4 * QP + V] * (cur[3 * 4 * QP + col] - dot);
+			float o = 0.f;
+#pragma unroll
+			for (int i = 0; i < Q; ++i) {
+				S[i] = fmaf(ks[i], u, S[i]);
+				o = fmaf(S[i], qs[i], o);
+			}
+			o += __shfl_xor_sync(0xffffffffu, o, 1);
+			o += __shfl_xor_sync(0xffffffffu, o, 2);
+			if (part == 0 && live) a.o[((size_t)n * a.heads + h) * V + col] = o;
+		}
+		if (more) {
+#pragma unroll
+			for (int r = 0; r < 2; ++r)
+				if (tid + r * (int)blockDim.x < items) put(nxt, tid + r * blockDim.x, pre[r]);
+		}
+		__syncthreads();
+	}
+	if (live) {
+#pragma unroll
+		for (int i = 0; i < Q; ++i) Sg[(size_t)(part * Q + i) * V + col] = S[i];
+	}
 }
 // read-out: o / rms(o) (per head) * w * sigmoid(gate); one warp per (token, head)
 template <typename AT>
@@ -487,6 +733,59 @@ __global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
 			gemm_store<bf16>(a, z, n, m, acc[i][j][0]), gemm_store<bf16>(a, z, n, m + 1, acc[i][j][1]);
 			gemm_store<bf16>(a, z, n + 8, m, acc[i][j][2]), gemm_store<bf16>(a, z, n + 8, m + 1, acc[i][j][3]);
 		}
+}
+
+// Few tokens (decode): every weight is used once, so the kernel is a stream over W.  A CTA owns 16 weight rows, its 8 warps
+// take interleaved 32-wide slices of K; a lane loads 16 bytes of row g and of row g + 8 per slice straight into the A
+// fragments of two m16n8k16 MMAs (the k order inside a slice is permuted the same way for A and B, which a sum over k does
+// not see); tokens are the MMA's N.  The warps' partial tiles are added in warp order through shared memory.
+template <int NT>
+__global__ void __launch_bounds__(256) k_seq_gemm_skinny(GemmArgs a) {
+	__shared__ float red[8][16][NT * 8 + 1];
+	const int z = blockIdx.z, m0 = blockIdx.x * 16, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
+	const bf16* W = a.W + (size_t)z * a.wbs;
+	const bf16* w0 = W + (size_t)min(m0 + g, a.M - 1) * a.ldw;
+	const bf16* w1 = W + (size_t)min(m0 + g + 8, a.M - 1) * a.ldw;
+	float acc[NT][4] = {};
+	const int nslice = (a.K + 31) / 32;
+	constexpr int U = 4; // slices requested before the first is used: 8 x 16 bytes in flight per lane
+	for (int s0 = warp; s0 < nslice; s0 += 8 * U) {
+		uint4 A0[U], A1[U];
+#pragma unroll
+		for (int u = 0; u < U; ++u) {
+			const int k = (s0 + 8 * u) * 32 + 8 * t;
+			A0[u] = A1[u] = make_uint4(0, 0, 0, 0);
+			if (k < a.K) A0[u] = __ldcs((const uint4*)(w0 + k)), A1[u] = __ldcs((const uint4*)(w1 + k));
+		}
+#pragma unroll
+		for (int u = 0; u < U; ++u) {
+			const int k = (s0 + 8 * u) * 32 + 8 * t;
+			const uint32_t F0[4] = {A0[u].x, A1[u].x, A0[u].y, A1[u].y}, F1[4] = {A0[u].z, A1[u].z, A0[u].w, A1[u].w};
+#pragma unroll
+			for (int j = 0; j < NT; ++j) {
+				uint4 B = make_uint4(0, 0, 0, 0);
+				const int n = j * 8 + g;
+				if (n < a.N && k < a.K) B = *(const uint4*)(X + (size_t)n * a.ldx + k);
+				const uint32_t B0[2] = {B.x, B.y}, B1[2] = {B.z, B.w};
+				mma_bf16_16816(acc[j], F0, B0);
+				mma_bf16_16816(acc[j], F1, B1);
+			}
+		}
+	}
+#pragma unroll
+	for (int j = 0; j < NT; ++j) {
+		red[warp][g][j * 8 + 2 * t] = acc[j][0], red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+		red[warp][g + 8][j * 8 + 2 * t] = acc[j][2], red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+	}
+	__syncthreads();
+	for (int i = tid; i < 16 * NT * 8; i += 256) {
+		const int n = i / 16, r = i % 16; // consecutive threads: consecutive weight rows of one token
+		float v = 0.f;
+#pragma unroll
+		for (int w = 0; w < 8; ++w) v += red[w][r][n];
+		gemm_store<bf16>(a, z, n, m0 + r, v);
+	}
 }
 
 // ---------------------------------------------------------------- sampling helper

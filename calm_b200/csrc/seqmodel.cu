@@ -17,8 +17,8 @@ namespace {
 
 uint64_t g_seq_launches = 0;
 
-enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_COUNT };
-const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise"};
+enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_GEMM_SKINNY, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_COUNT };
+const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "gemm_skinny", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise"};
 
 // what one run of a layer owns (a looped layer has one of these per pass)
 struct RunState {
@@ -62,6 +62,17 @@ struct Seq {
 	float *x = nullptr, *x0 = nullptr, *proj = nullptr, *f[6] = {};
 	void *hA = nullptr, *a1 = nullptr, *a2 = nullptr; // activation type (float or bf16)
 	size_t w_proj = 0, w_f = 0, w_a = 0;              // widths (elements per token)
+	// prompt attention as products: gathered keys / transposed values of one key head, scores and probabilities
+	bool attn_products = true;
+	bf16 *att_kb = nullptr, *att_vt = nullptr, *att_p = nullptr;
+	float* att_s = nullptr;
+	size_t cap_kb = 0, cap_vt = 0, cap_sp = 0;
+	void* a3 = nullptr;                               // queries in the activation type
+	std::vector<int> hb_start, hb_count, hb_pos0, hb_slot; // host copy of the batch description
+	int* d_skip = nullptr;                            // [N] 1: token served by the product path
+	int n_on_products = 0, tok_on_products = 0;       // sequences / tokens of this step on the product path
+	float* part = nullptr; // partial attention results of key-split launches
+	size_t part_cap = 0;
 	float* logits = nullptr;
 	void* hW = nullptr; // normed rows of the wanted tokens
 	int last_want = 0, last_tokens = 0;
@@ -114,15 +125,16 @@ int conv_channels(const SeqLayer& L) {
 }
 // query heads per CTA of the attention kernel: divides the group, keeps the accumulators in registers and the queries in shared memory
 int attn_tile(int group, int kd, int vd) {
+	if (vd > 2 * ATT_THREADS) return 1; // wide values: one head per CTA
 	int t = group;
-	while (t > 1 && ((size_t)t * vd > (size_t)ATT_MAXI * ATT_THREADS || (size_t)t * (kd + ATT_KC + 3) * sizeof(float) > 96 * 1024 || t > 16)) {
+	while (t > 1 && ((size_t)t * (kd + ATT_KC + 3) * sizeof(float) > 96 * 1024 || t > 16)) {
 		int d = t - 1;
 		while (group % d) --d;
 		t = d;
 	}
 	return t;
 }
-size_t attn_smem(int tile, int kd) { return (size_t)tile * (kd + ATT_KC + 3) * sizeof(float); }
+size_t attn_smem(int tile, int kd) { return ((size_t)tile * (kd + ATT_KC + 3) + 4) * sizeof(float); }
 
 void validate(const Seq& s) {
 	const SeqModel& m = s.m;
@@ -134,7 +146,7 @@ void validate(const Seq& s) {
 		if (L.heads < 1 || L.dim < 1 || L.vdim < 1) CALM_FATAL("seq: layer %d: heads, dim and vdim must be positive", i);
 		if (L.type == SEQ_LATENT) {
 			if (L.q_rank < 1 || L.kv_rank < 1) CALM_FATAL("seq: layer %d: latent ranks must be positive", i);
-			if ((size_t)L.kv_rank > (size_t)ATT_MAXI * ATT_THREADS) CALM_FATAL("seq: layer %d: kv_rank %d is more than the attention kernel holds", i, L.kv_rank);
+			if (cdiv(L.kv_rank, ATT_THREADS) > ATT_MAXI) CALM_FATAL("seq: layer %d: kv_rank %d is more than the attention kernel holds", i, L.kv_rank);
 		} else if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW) {
 			if (L.kv_heads < 1 || L.heads % L.kv_heads) CALM_FATAL("seq: layer %d: heads must be a multiple of kv_heads", i);
 			if (L.taps < 1) CALM_FATAL("seq: layer %d: taps must be positive", i);
@@ -142,7 +154,7 @@ void validate(const Seq& s) {
 				if (L.vdim > 1024) CALM_FATAL("seq: layer %d: vdim above 1024", i);
 				if (((size_t)L.dim * L.vdim + 3 * (size_t)L.dim) * sizeof(float) > 227 * 1024) CALM_FATAL("seq: layer %d: a %d x %d state does not fit shared memory", i, L.dim, L.vdim);
 				if (L.a_rank < 1 || L.g_rank < 1) CALM_FATAL("seq: layer %d: decay and gate ranks must be positive", i);
-			} else if ((size_t)L.vdim > (size_t)ATT_MAXI * ATT_THREADS) CALM_FATAL("seq: layer %d: vdim too large", i);
+			} else if (cdiv(L.vdim, ATT_THREADS) > ATT_MAXI) CALM_FATAL("seq: layer %d: vdim too large", i);
 		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
 	}
 }
@@ -152,9 +164,9 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		const int cn = std::max(N, s.cap_tokens), cb = std::max(B, s.cap_seqs);
 		CUDA_CHECK(cudaStreamSynchronize(s.stream));
 		cudaFree(s.d_tok);
-		s.d_tok = (int*)dalloc(((size_t)4 * cn + 4 * cb) * sizeof(int));
-		s.d_tslot = s.d_tok + cn, s.d_tpos = s.d_tslot + cn, s.d_tfirst = s.d_tpos + cn;
-		s.d_sstart = s.d_tfirst + cn, s.d_scount = s.d_sstart + cb, s.d_spos0 = s.d_scount + cb, s.d_sslot = s.d_spos0 + cb;
+		s.d_tok = (int*)dalloc(((size_t)5 * cn + 4 * cb) * sizeof(int));
+		s.d_tslot = s.d_tok + cn, s.d_tpos = s.d_tslot + cn, s.d_tfirst = s.d_tpos + cn, s.d_skip = s.d_tfirst + cn;
+		s.d_sstart = s.d_skip + cn, s.d_scount = s.d_sstart + cb, s.d_spos0 = s.d_scount + cb, s.d_sslot = s.d_spos0 + cb;
 		s.cap_seqs = cb;
 	}
 	if (W > s.cap_want) {
@@ -168,7 +180,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 	}
 	if (N > s.cap_tokens) {
 		const size_t cn = N;
-		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2);
+		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2), cudaFree(s.a3);
 		for (float*& p : s.f) cudaFree(p);
 		s.x = (float*)dalloc(cn * s.m.width * sizeof(float));
 		s.x0 = (float*)dalloc(cn * s.m.width * sizeof(float));
@@ -177,6 +189,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		s.hA = dalloc(cn * s.m.width * act_size(s));
 		s.a1 = dalloc(cn * s.w_a * act_size(s));
 		s.a2 = dalloc(cn * s.w_a * act_size(s));
+		s.a3 = dalloc(cn * s.w_a * act_size(s));
 		s.cap_tokens = N;
 	}
 	if (s.trace && (size_t)N * s.runs.size() > (size_t)s.trace_cap) {
@@ -189,7 +202,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 // ---------------------------------------------------------------- launches
 
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
-          const SeqNorm* nrm = nullptr) {
+          const SeqNorm* nrm = nullptr, int kind_as = -1) {
 	GemmArgs a;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
@@ -197,11 +210,21 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	const double flops = 2.0 * N * M * K * batch;
 	const double bytes = ((double)M * K * 2 + (double)N * K * act_size(s) + (double)N * M * 4) * batch;
 	if (s.tc && gemm_tc_fits(a, batch)) {
-		run_kernel(s, KD_GEMM_TC, bytes, flops, [&] { gemm_tc_launch(a, s.stream); });
+		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_TC, bytes, flops, [&] { gemm_tc_launch(a, s.stream); });
+		return;
+	}
+	auto al8 = [](long v) { return v % 8 == 0; };
+	if (!s.m.exact && N <= 32 && K % 8 == 0 && al8(ldx) && al8(ldw) && al8(xbs) && al8(wbs) && ((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+		const dim3 grid(cdiv(M, 16), 1, batch);
+		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_SKINNY, bytes, flops, [&] {
+			if (N <= 8) k_seq_gemm_skinny<1><<<grid, 256, 0, s.stream>>>(a);
+			else if (N <= 16) k_seq_gemm_skinny<2><<<grid, 256, 0, s.stream>>>(a);
+			else k_seq_gemm_skinny<4><<<grid, 256, 0, s.stream>>>(a);
+		});
 		return;
 	}
 	const dim3 grid(cdiv(M, 64), cdiv(N, 64), batch);
-	run_kernel(s, KD_GEMM, bytes, flops, [&] {
+	run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM, bytes, flops, [&] {
 		if (s.m.exact) k_seq_gemm_f32<<<grid, 256, 0, s.stream>>>(a);
 		else k_seq_gemm_bf16<<<grid, 128, 0, s.stream>>>(a);
 	});
@@ -215,15 +238,87 @@ void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, 
 	});
 }
 
-void attention(Seq& s, int kind, const AttArgs& a, void* out, const SeqBatch& sb, double kv_rows) {
+// Sequences that bring at least this many tokens to a step have their attention computed as products (bf16 mode).
+const int kAttnGemmMin = 16;
+
+void reserve_attn(Seq& s, size_t kb, size_t vt, size_t sp) {
+	if (kb <= s.cap_kb && vt <= s.cap_vt && sp <= s.cap_sp) return;
+	CUDA_CHECK(cudaStreamSynchronize(s.stream));
+	if (kb > s.cap_kb) cudaFree(s.att_kb), s.att_kb = (bf16*)dalloc(kb * sizeof(bf16)), s.cap_kb = kb;
+	if (vt > s.cap_vt) cudaFree(s.att_vt), s.att_vt = (bf16*)dalloc(vt * sizeof(bf16)), s.cap_vt = vt;
+	if (sp > s.cap_sp) {
+		cudaFree(s.att_s), cudaFree(s.att_p);
+		s.att_s = (float*)dalloc(sp * sizeof(float)), s.att_p = (bf16*)dalloc(sp * sizeof(bf16)), s.cap_sp = sp;
+	}
+}
+
+// one sequence's new tokens [first, first + count) at positions pos0.., in blocks of queries that keep S within budget
+void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const SeqBatch& sb, int slot, int first, int count, int pos0) {
+	const int G = a.heads / a.group;
+	const size_t budget = (size_t)96 << 20; // elements of S per launch
+	for (int t0 = 0; t0 < count;) {
+		const int q0 = pos0 + t0;
+		int Tb = count - t0;
+		while (Tb > 64 && (size_t)a.group * Tb * (size_t)(q0 + Tb) > budget) Tb = (Tb + 1) / 2;
+		const int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0, C = q0 + Tb - k0, Cp = (C + 7) & ~7;
+		reserve_attn(s, (size_t)C * a.kd, (size_t)a.vd * Cp, (size_t)a.group * Tb * Cp);
+		for (int kvh = 0; kvh < G; ++kvh) {
+			AttGather g;
+			g.kc = a.kc, g.vc = a.vc, g.kld = a.kld, g.vld = a.vld, g.kcol = kvh * a.kd, g.vcol = kvh * a.vd, g.kd = a.kd, g.vd = a.vd;
+			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp;
+			run_kernel(s, kind, (double)C * (a.kd + a.vd) * 6, 0, [&] { k_seq_attn_gather<<<dim3(cdiv(Cp, 32), 4), 256, 0, s.stream>>>(g, sb); });
+			const int h0 = kvh * a.group;
+			const bf16* q = (const bf16*)s.a3 + ((size_t)(first + t0) * a.heads + h0) * a.kd;
+			gemm(s, q, (long)a.heads * a.kd, a.kd, s.att_kb, a.kd, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd, a.group, EPI_F32, nullptr, kind);
+			AttSoftmax sm;
+			sm.S = s.att_s, sm.P = s.att_p, sm.T = Tb, sm.C = C, sm.Cp = Cp, sm.qpos0 = q0, sm.k0 = k0, sm.window = a.window, sm.scale = a.scale;
+			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = a.gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
+			run_kernel(s, kind, (double)a.group * Tb * Cp * 6, 0, [&] { k_seq_attn_softmax<<<dim3(Tb, a.group), 256, 0, s.stream>>>(sm); });
+			gemm(s, s.att_p, Cp, (long)Tb * Cp, s.att_vt, Cp, 0, out + ((size_t)(first + t0) * a.heads + h0) * a.vd, (long)a.heads * a.vd, a.vd, Tb, a.vd, C, a.group,
+			     EPI_ACT, nullptr, kind);
+		}
+		t0 += Tb;
+	}
+}
+
+void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, double kv_rows, int longest) {
+	a.skip = nullptr;
+	bool rest = true;
+	if (!s.m.exact && s.attn_products && s.n_on_products > 0) {
+		const size_t n = (size_t)sb.N * a.heads * a.kd;
+		run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { k_seq_cast_cols<bf16><<<cdiv(n, 256), 256, 0, s.stream>>>((bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
+		for (int b = 0; b < sb.B; ++b)
+			if (s.hb_count[b] >= kAttnGemmMin) attention_products(s, kind, a, (bf16*)out, sb, s.hb_slot[b], s.hb_start[b], s.hb_count[b], s.hb_pos0[b]);
+		a.skip = s.d_skip;
+		rest = s.n_on_products < sb.B;
+	}
+	if (!rest) return;
 	const size_t smem = attn_smem(a.tile, a.kd);
-	const dim3 grid(sb.N, a.heads / a.tile);
+	// few tokens over a long context: the keys of one (token, head tile) are shared out over several CTAs
+	const int live = a.skip ? std::max(1, sb.N - s.tok_on_products) : sb.N; // tokens the fused kernel really serves (the others' CTAs leave at once)
+	const int ctas = live * (a.heads / a.tile), chunks = cdiv(a.window > 0 ? std::min(longest, a.window) : longest, ATT_KC);
+	a.nsplit = ctas >= 2 * s.sms ? 1 : std::max(1, std::min({chunks / 2, 2 * s.sms / ctas, 64}));
+	if (a.nsplit > 1) {
+		const size_t need = (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2);
+		if (need > s.part_cap) {
+			CUDA_CHECK(cudaStreamSynchronize(s.stream));
+			cudaFree(s.part);
+			s.part = (float*)dalloc(need * sizeof(float)), s.part_cap = need;
+		}
+	}
+	a.part = s.part;
+	const dim3 grid(sb.N, a.heads / a.tile, a.nsplit);
 	const double bytes = kv_rows * (a.heads / a.group) * (a.kc == a.vc ? a.kd : a.kd + a.vd) * 4.0;
 	const double flops = 2.0 * kv_rows * a.heads * (a.kd + a.vd);
-	run_kernel(s, kind, bytes, flops, [&] {
+	run_kernel(s, kind, a.skip ? 0 : bytes, a.skip ? 0 : flops, [&] {
 		if (s.m.exact) k_seq_attention<float><<<grid, ATT_THREADS, smem, s.stream>>>(a, (float*)out, sb);
 		else k_seq_attention<bf16><<<grid, ATT_THREADS, smem, s.stream>>>(a, (bf16*)out, sb);
 	});
+	if (a.nsplit > 1)
+		run_kernel(s, kind, 0, 0, [&] {
+			if (s.m.exact) k_seq_attention_merge<float><<<dim3(sb.N, a.heads), 128, 0, s.stream>>>(a, (float*)out);
+			else k_seq_attention_merge<bf16><<<dim3(sb.N, a.heads), 128, 0, s.stream>>>(a, (bf16*)out);
+		});
 }
 
 void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& sb) {
@@ -236,7 +331,7 @@ void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& 
 }
 
 template <typename AT>
-void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows) {
+void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest) {
 	const int N = sb.N, W = s.m.width, P = (int)in_rows(L);
 	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
 	gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, P, W, 1, EPI_F32);
@@ -251,7 +346,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		AttArgs a;
 		a.q = s.f[0], a.kc = a.vc = r.cache_a, a.kld = a.vld = Rk, a.heads = H, a.group = H, a.tile = attn_tile(H, Rk, Rk), a.kd = a.vd = Rk, a.window = 0;
 		a.scale = L.scale, a.sink = nullptr, a.gate = s.proj + Rq + Rk, a.ldg = P;
-		attention(s, KD_ATTN_LATENT, a, a1, sb, kv_rows);
+		attention(s, KD_ATTN_LATENT, a, a1, sb, kv_rows, longest);
 		gemm(s, a1, (long)H * Rk, Rk, L.w_uv, Rk, (long)Dv * Rk, a2, (long)H * Dv, Dv, N, Dv, Rk, H, EPI_ACT);
 		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
 	} else if (L.type == SEQ_DELTA) {
@@ -272,8 +367,15 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		d.state = r.delta, d.o = s.f[5], d.heads = H, d.kv_heads = G, d.dim = D, d.vdim = Dv;
 		const size_t smem = ((size_t)D * Dv + 3 * D) * sizeof(float);
 		const int threads = std::max(64, cdiv(Dv, 32) * 32);
-		run_kernel(s, KD_DELTA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 6.0,
-		           [&] { k_seq_delta_scan<<<dim3(sb.B, H), threads, smem, s.stream>>>(d, sb); });
+		const size_t smem_reg = 2 * (size_t)(3 * (D + 4) + Dv + 1) * sizeof(float);
+		const int threads_reg = std::max(256, cdiv(4 * Dv, 32) * 32); // two staging rounds cover 3 D + Dv + 1 items
+		const bool reg = (D == 32 || D == 64 || D == 128) && 4 * Dv <= 512 && !getenv("CALM_B200_SEQ_DELTA_SMEM");
+		run_kernel(s, KD_DELTA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 6.0, [&] {
+			if (reg && D == 32) k_seq_delta_scan_reg<32><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
+			else if (reg && D == 64) k_seq_delta_scan_reg<64><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
+			else if (reg && D == 128) k_seq_delta_scan_reg<128><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
+			else k_seq_delta_scan<<<dim3(sb.B, H), threads, smem, s.stream>>>(d, sb);
+		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
 		           [&] { k_seq_delta_out<AT><<<cdiv((long)N * H, 4), 128, 0, s.stream>>>(a2, s.f[5], s.f[4], (const bf16*)L.out_norm, N, H, Dv, s.m.eps); });
 		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
@@ -287,7 +389,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		AttArgs a;
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
 		a.window = L.window, a.scale = L.scale, a.sink = (const bf16*)L.sink, a.gate = nullptr, a.ldg = 0;
-		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * L.window) : kv_rows);
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * L.window) : kv_rows, longest);
 		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
 	}
 	if (L.ff > 0) {
@@ -329,6 +431,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	CUDA_CHECK(cudaStreamCreate(&s.stream));
 	for (cudaEvent_t& e : s.ev) CUDA_CHECK(cudaEventCreate(&e));
 	for (cudaEvent_t& e : s.timer) CUDA_CHECK(cudaEventCreate(&e));
+	if (const char* e = getenv("CALM_B200_SEQ_ATTN_PRODUCTS")) s.attn_products = atoi(e) != 0;
 	const char* tc = getenv("CALM_B200_SEQ_TC");
 	s.tc = !s.m.exact && !(tc && atoi(tc) == 0);
 	if (s.tc) gemm_tc_setup();
@@ -380,7 +483,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		size_t wf = 0, wa = (size_t)L.ff;
 		if (L.type == SEQ_LATENT) wf = (size_t)L.heads * L.kv_rank, wa = std::max({wa, (size_t)L.heads * L.kv_rank, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim, (size_t)L.q_rank});
 		if (L.type == SEQ_DELTA) wf = std::max((size_t)L.heads * L.dim, (size_t)L.heads * L.vdim), wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.a_rank + L.g_rank});
-		if (L.type == SEQ_WINDOW) wf = (size_t)L.heads * L.dim, wa = std::max(wa, (size_t)L.heads * L.vdim);
+		if (L.type == SEQ_WINDOW) wf = (size_t)L.heads * L.dim, wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim});
 		s.w_f = std::max(s.w_f, wf), s.w_a = std::max(s.w_a, wa);
 	}
 	return sp;
@@ -392,7 +495,7 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	cudaStreamSynchronize(s->stream);
 	for (RunState& r : s->runs) cudaFree(r.cache_a), cudaFree(r.cache_b), cudaFree(r.conv), cudaFree(r.delta);
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
-	cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
+	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);
 	for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
 	for (cudaEvent_t e : s->timer) cudaEventDestroy(e);
@@ -450,10 +553,13 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 
 	// pages for the new tokens, then the batch description
 	double kv_rows = 0; // cache rows the causal attentions read this step
-	s.h_meta.resize((size_t)4 * N + 4 * n_seq);
-	int *tok = s.h_meta.data(), *tslot = tok + N, *tpos = tslot + N, *tfirst = tpos + N, *sstart = tfirst + N, *scount = sstart + n_seq, *spos0 = scount + n_seq,
+	int longest = 0;    // longest sequence after this step
+	s.h_meta.resize((size_t)5 * N + 4 * n_seq);
+	int *tok = s.h_meta.data(), *tslot = tok + N, *tpos = tslot + N, *tfirst = tpos + N, *skip = tfirst + N, *sstart = skip + N, *scount = sstart + n_seq, *spos0 = scount + n_seq,
 	    *sslot = spos0 + n_seq;
 	int at = 0;
+	s.hb_start.resize(n_seq), s.hb_count.resize(n_seq), s.hb_pos0.resize(n_seq), s.hb_slot.resize(n_seq);
+	s.n_on_products = s.tok_on_products = 0;
 	for (int b = 0; b < n_seq; ++b) {
 		Slot& sl = s.slots[slots[b]];
 		const size_t had = sl.pages.size();
@@ -466,13 +572,17 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 			CUDA_CHECK(cudaMemcpyAsync(s.table_dev + o, s.table.data() + o, (sl.pages.size() - had) * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 		}
 		sstart[b] = at, scount[b] = counts[b], spos0[b] = sl.len, sslot[b] = slots[b];
-		for (int t = 0; t < counts[b]; ++t, ++at) tok[at] = tokens[at], tslot[at] = slots[b], tpos[at] = sl.len + t, tfirst[at] = sstart[b], kv_rows += sl.len + t + 1;
+		for (int t = 0; t < counts[b]; ++t, ++at) tok[at] = tokens[at], tslot[at] = slots[b], tpos[at] = sl.len + t, tfirst[at] = sstart[b], skip[at] = counts[b] >= kAttnGemmMin, kv_rows += sl.len + t + 1;
+		s.hb_start[b] = sstart[b], s.hb_count[b] = counts[b], s.hb_pos0[b] = sl.len, s.hb_slot[b] = slots[b];
+		if (counts[b] >= kAttnGemmMin) ++s.n_on_products, s.tok_on_products += counts[b];
 		sl.len += counts[b];
+		longest = std::max(longest, sl.len);
 	}
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tok, tok, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tslot, tslot, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tpos, tpos, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_tfirst, tfirst, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
+	CUDA_CHECK(cudaMemcpyAsync(s.d_skip, skip, N * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_sstart, sstart, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_scount, scount, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
 	CUDA_CHECK(cudaMemcpyAsync(s.d_spos0, spos0, n_seq * sizeof(int), cudaMemcpyHostToDevice, s.stream));
@@ -493,8 +603,8 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { k_seq_add<<<cdiv(n, 256), 256, 0, s.stream>>>(s.x, s.x0, n); });
 		}
 		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
-		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows);
-		else mixer_typed<bf16>(s, L, r, sb, kv_rows);
+		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows, longest);
+		else mixer_typed<bf16>(s, L, r, sb, kv_rows, longest);
 		if (s.trace)
 			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
 	}
