@@ -15,9 +15,9 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(HERE, "..", "include")
 TARGETS = {
     "engine": {"lib": os.path.join(HERE, "libcalm_b200.so"), "sources": ["engine.cu"],
-               "deps": ["attn.cuh", "common.cuh", "prefill.cuh", "ring.cuh", "stages.cuh", os.path.join(INCLUDE, "calm_b200.h"), os.path.join(INCLUDE, "calm_model.h")]},
+               "deps": ["attn.cuh", "common.cuh", "tc05.cuh", "prefill.cuh", "ring.cuh", "stages.cuh", os.path.join(INCLUDE, "calm_b200.h"), os.path.join(INCLUDE, "calm_model.h")]},
     "seq": {"lib": os.path.join(HERE, "libcalm_b200_seq.so"), "sources": ["seqmodel.cu"],
-            "deps": ["common.cuh", "seqkernels.cuh", "seqgemm_tc.cuh", os.path.join(INCLUDE, "calm_b200_seq.h")]},
+            "deps": ["common.cuh", "tc05.cuh", "seqkernels.cuh", "seqgemm_tc.cuh", os.path.join(INCLUDE, "calm_b200_seq.h")]},
 }
 LIB = TARGETS["engine"]["lib"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include "stages.cuh"
+#include "tc05.cuh"
 
 #define PF_BM 128 // weight rows per tile  (TMEM lanes)
 #define PF_BN 128 // tokens per tile       (TMEM columns per accumulator)
@@ -30,73 +31,6 @@
 #define PF_THREADS 192
 enum { PF_QKV = 0, PF_WO = 1, PF_UP = 2, PF_DOWN = 3 };
 
-// ---------------------------------------------------------------- tcgen05 / TMA wrappers
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) { // one whole warp
-	asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
-	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) { // the allocating warp
-	asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// D[tmem] (+)= A[smem] . B[smem]^T, f16 x f16 -> f32, issued by ONE thread
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-	asm volatile(
-	    "{\n\t.reg .pred p;\n\t"
-	    "setp.ne.b32 p, %4, 0;\n\t"
-	    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-	    ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-	    : "memory");
-}
-// all MMAs issued so far by this thread arrive on `bar` when they have completed (implies fence::before_thread_sync)
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// 32 lanes x 32 columns of 32-bit accumulators: thread t of the warp gets row (lane base + t), columns c .. c+31
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-	uint32_t r[32];
-	asm volatile(
-	    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-	    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-	      "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
-	      "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-	    : "r"(taddr)
-	    : "memory");
-	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-	for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-	asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)), "l"(map),
-	             "r"(c0), "r"(c1), "r"(smem_u32(bar))
-	             : "memory");
-}
-// bounded wait (about 2 s): a broken pipeline traps with a message instead of hanging the GPU
-__device__ __forceinline__ void mbar_wait_guard(uint64_t* bar, uint32_t parity) {
-	unsigned spins = 0;
-	while (!mbar_try_wait(bar, parity)) {
-		if (++spins > (1u << 26)) {
-			printf("calm_b200: k_pf_gemm pipeline stalled (block %d,%d thread %d)\n", blockIdx.x, blockIdx.y, threadIdx.x);
-			__trap();
-		}
-	}
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { // generic-proxy writes to shared memory -> visible to the async proxy (tensor core reads)
-	asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-// shared-memory matrix descriptor: K-major tile, rows of 128 bytes (64 f16), SWIZZLE_128B, 8-row groups 1024 bytes apart, sm_100 version bit
-__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
-	const uint64_t addr = (uint64_t)(smem_u32(tile) & 0x3FFFF) >> 4;
-	return addr | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
 // instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = 128
 #define PF_IDESC ((1u << 4) | ((uint32_t)(PF_BN >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24))
 

@@ -210,8 +210,9 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	const double flops = 2.0 * N * M * K * batch;
 	const double bytes = ((double)M * K * 2 + (double)N * K * act_size(s) + (double)N * M * 4) * batch;
 	if (s.tc && gemm_tc_fits(a, batch)) {
-		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_TC, bytes, flops, [&] { gemm_tc_launch(a, s.stream); });
-		return;
+		bool launched = false;
+		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_TC, bytes, flops, [&] { launched = gemm_tc_launch(a, batch, s.stream); });
+		if (launched) return;
 	}
 	auto al8 = [](long v) { return v % 8 == 0; };
 	if (!s.m.exact && N <= 32 && K % 8 == 0 && al8(ldx) && al8(ldw) && al8(xbs) && al8(wbs) && ((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0) {
@@ -615,6 +616,7 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 		if (logits_host) CUDA_CHECK(cudaMemcpyAsync(logits_host, s.logits, (size_t)n_want * m.vocab * sizeof(float), cudaMemcpyDeviceToHost, s.stream));
 	}
 	CUDA_CHECK(cudaStreamSynchronize(s.stream));
+	if (int code = gemm_tc_error()) CALM_FATAL("seq: the tensor-core product pipeline stalled (code %d)", code);
 	return 0;
 }
 

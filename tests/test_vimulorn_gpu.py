@@ -209,6 +209,28 @@ def test_prompt_attention_as_products_matches_the_fused_kernel(monkeypatch):
         assert rel_err(plain.forward(wrong, as_f64(t), toks), ref) > 4 * errs["1"]
 
 
+def test_tensor_core_products_match_the_warp_level_ones(monkeypatch):
+    """bfloat16 mode runs products over many tokens on tcgen05 (TMA-fed, TMEM accumulators) and everything else on mma.sync;
+    same bf16 inputs, fp32 sums in another order.  Sizes include edges that do not fill a tile in M, N or K."""
+    cfg = config([latent(heads=4, dim=32, vdim=24, kv_rank=72, q_rank=40), delta(heads=2, kv_heads=1, dim=32, vdim=40), window(size=50)], width=88, vocab=131)
+    t, toks = weights(cfg, 17), tokens(cfg, 200)
+    outs = {}
+    for tc in ("1", "0"):
+        monkeypatch.setenv("CALM_B200_SEQ_TC", tc)
+        with vimulorn.from_tensors(cfg, t, "bfloat16", max_tokens=512, max_seqs=2, page=16) as m:
+            s1 = m.open()
+            outs[tc] = np.concatenate([m.step([s1], [toks[:137]], list(range(137))), m.step([s1], [toks[137:]], list(range(63)))])
+            stats = None
+            if tc == "1":
+                m.perf(True)
+                whole(m, toks)
+                stats = m.perf_stats()
+                m.perf(False)
+                assert stats["gemm_tcgen05"][3] > 0
+    assert rel_err(outs["1"], outs["0"]) < 2e-3  # identical inputs; intermediate bf16 roundings may flip on last-bit differences
+    assert rel_err(outs["1"], plain.forward(cfg, as_f64(t), toks)) < TOL["bfloat16"]
+
+
 def test_long_decoding_keeps_state():
     cfg = config([delta(conv=3), window(size=12, conv=3)])
     t, toks = weights(cfg, 14), tokens(cfg, 130)
