@@ -518,77 +518,124 @@ __global__ void k_seq_delta_scan(DeltaArgs a, SeqBatch sb) {
 	__syncthreads();
 	for (int i = tid; i < D * V; i += blockDim.x) Sg[i] = S[i];
 }
-// The same recurrence with the state in registers: four lanes share a value column, each holding D/4 of its rows; the
-// next token's k, q, decay, v and beta are staged into the other half of a double buffer while the current token is
-// applied (one barrier per token).
+// The same recurrence with the state in registers: four lanes share a value column, each holding D/4 of its rows.  Tokens are
+// staged DELTA_TB at a time: while one block of tokens is applied (no barrier between its tokens, only shuffles inside a
+// column's four lanes), the next block's k, q, decay, v and beta travel from global memory into the other half of a double
+// buffer; k, q and the decay are read back as float4 (quarters padded by 4 floats: the four lanes hit different banks).
+#define DELTA_TB 4
 template <int D>
 __global__ void __launch_bounds__(512) k_seq_delta_scan_reg(DeltaArgs a, SeqBatch sb) {
-	constexpr int Q = D / 4, QP = Q + 1; // padded quarter: the four lanes of a column read different banks
-	extern __shared__ float sm[];
+	constexpr int Q = D / 4, QP = Q + 4;
+	extern __shared__ __align__(16) float sm[];
 	const int b = blockIdx.x, h = blockIdx.y, V = a.vdim;
 	const int kh = h / (a.heads / a.kv_heads);
 	const int tid = threadIdx.x, part = tid & 3;
 	const bool live = (tid >> 2) < V;          // lanes past the last column run along on a copy of it (whole warps shuffle)
 	const int col = live ? tid >> 2 : V - 1;
-	const int stage_len = 3 * 4 * QP + V + 1; // k, q, g (padded quarters), v, beta
-	float* buf[2] = {sm, sm + stage_len};
+	const int vpad = (V + 1 + 3) & ~3;         // v and beta of a token, rounded so that the next token stays 16-byte aligned
+	const int tok_len = 3 * 4 * QP + vpad;     // k, q, g (padded quarters), v, beta
+	float* buf[2] = {sm, sm + DELTA_TB * tok_len};
 	float S[Q];
 	float* Sg = a.state + ((size_t)sb.sslot[b] * a.heads + h) * D * V;
 #pragma unroll
 	for (int i = 0; i < Q; ++i) S[i] = Sg[(size_t)(part * Q + i) * V + col];
 	const float A = expf(ldf(a.a_log + h));
 	const int start = sb.sstart[b], cnt = sb.scount[b];
-	// item `it` of a token's stage: [0, D) k, [D, 2D) q, [2D, 3D) decay, [3D, 3D + V) v, 3D + V beta
-	auto fetch = [&](int n, int it) -> float {
-		if (it < D) return a.k[((size_t)n * a.kv_heads + kh) * D + it];
-		if (it < 2 * D) return a.q[((size_t)n * a.kv_heads + kh) * D + it - D];
-		if (it < 3 * D) return expf(-A * softplusf_(a.dt[((size_t)n * a.heads + h) * D + it - 2 * D] + ldf(a.dt_bias + h * D + it - 2 * D)));
-		if (it < 3 * D + V) return a.v[((size_t)n * a.heads + h) * V + it - 3 * D];
-		return sigmoidf_(a.proj[(size_t)n * a.ldp + a.bcol + h]);
-	};
-	auto put = [&](float* st, int it, float v) {
-		if (it < 3 * D) st[(it / D) * 4 * QP + ((it % D) / Q) * QP + (it % D) % Q] = v;
-		else st[3 * 4 * QP + it - 3 * D] = v;
-	};
-	const int items = 3 * D + V + 1;
-	for (int it = tid; it < items; it += blockDim.x) put(buf[0], it, fetch(start, it));
-	__syncthreads();
-	for (int t = 0; t < cnt; ++t) {
-		const int n = start + t;
-		float* cur = buf[t & 1];
-		float* nxt = buf[(t + 1) & 1];
-		float pre[2];
-		const bool more = t + 1 < cnt;
-		if (more) {
+	// Staging.  A token's inputs are 3 D / 4 + V / 4 float4 items (k, q, raw decay input, v) and one scalar (beta's input); item e of a
+	// block belongs to token e / items4.  Thread tid serves items tid and tid + blockDim of every block, so where an item comes from
+	// and where it goes is worked out once; per block a thread issues its (at most two) 16-byte loads before the running block's
+	// arithmetic and finishes them (decay, beta) into the other buffer after it.
+	const int items4 = (3 * D + V) / 4 + 1;
+	const float* src[2];
+	const bf16* biasp[2];            // decay items: their four dt_bias entries
+	int stride[2], slot[2], kind[2]; // kind: 0 plain float4, 1 decay input, 2 beta input (scalar), -1 none
 #pragma unroll
-			for (int r = 0; r < 2; ++r) pre[r] = tid + r * (int)blockDim.x < items ? fetch(n + 1, tid + r * blockDim.x) : 0.f;
+	for (int r = 0; r < 2; ++r) {
+		const int e = tid + r * (int)blockDim.x, tt = e / items4, it4 = e % items4;
+		kind[r] = -1, src[r] = a.k, stride[r] = 0, slot[r] = 0, biasp[r] = a.dt_bias;
+		if (tt < DELTA_TB) {
+			const int i0 = 4 * it4;
+			if (i0 < 3 * D) {
+				const int seg = i0 / D, w = i0 % D;
+				kind[r] = seg == 2 ? 1 : 0;
+				biasp[r] = a.dt_bias + h * D + w;
+				stride[r] = seg == 2 ? a.heads * D : a.kv_heads * D;
+				src[r] = (seg == 0 ? a.k + (size_t)kh * D : seg == 1 ? a.q + (size_t)kh * D : a.dt + (size_t)h * D) + w + (size_t)(start + tt) * stride[r];
+				slot[r] = tt * tok_len + seg * 4 * QP + (w / Q) * QP + w % Q;
+			} else if (i0 < 3 * D + V) {
+				kind[r] = 0, stride[r] = a.heads * V;
+				src[r] = a.v + (size_t)h * V + (i0 - 3 * D) + (size_t)(start + tt) * stride[r];
+				slot[r] = tt * tok_len + 3 * 4 * QP + i0 - 3 * D;
+			} else {
+				kind[r] = 2, stride[r] = a.ldp;
+				src[r] = a.proj + a.bcol + h + (size_t)(start + tt) * stride[r];
+				slot[r] = tt * tok_len + 3 * 4 * QP + V;
+			}
 		}
-		{
-			const float *ks = cur + part * QP, *qs = cur + 4 * QP + part * QP, *gs = cur + 8 * QP + part * QP;
+	}
+	const int tt_of[2] = {tid / items4, (tid + (int)blockDim.x) / items4};
+	auto fetch_block = [&](int blk, float4 (&pre)[2]) {
+		const int nt = min(DELTA_TB, cnt - blk * DELTA_TB);
+#pragma unroll
+		for (int r = 0; r < 2; ++r) {
+			pre[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+			if (kind[r] >= 0 && tt_of[r] < nt) {
+				const float* p = src[r] + (size_t)blk * DELTA_TB * stride[r];
+				if (kind[r] == 2) pre[r].x = __ldg(p);
+				else pre[r] = __ldg((const float4*)p);
+			}
+		}
+	};
+	auto put_block = [&](float* st, int blk, const float4 (&pre)[2]) {
+		const int nt = min(DELTA_TB, cnt - blk * DELTA_TB);
+#pragma unroll
+		for (int r = 0; r < 2; ++r) {
+			if (kind[r] >= 0 && tt_of[r] < nt) {
+				float4 v = pre[r];
+				if (kind[r] == 1) {
+					const bf16* bias = biasp[r];
+					v.x = expf(-A * softplusf_(v.x + ldf(bias))), v.y = expf(-A * softplusf_(v.y + ldf(bias + 1)));
+					v.z = expf(-A * softplusf_(v.z + ldf(bias + 2))), v.w = expf(-A * softplusf_(v.w + ldf(bias + 3)));
+				}
+				if (kind[r] == 2) st[slot[r]] = sigmoidf_(v.x);
+				else *(float4*)(st + slot[r]) = v;
+			}
+		}
+	};
+	const int nblk = (cnt + DELTA_TB - 1) / DELTA_TB;
+	float4 pre[2];
+	fetch_block(0, pre);
+	put_block(buf[0], 0, pre);
+	__syncthreads();
+	for (int blk = 0; blk < nblk; ++blk) {
+		const float* cur = buf[blk & 1];
+		if (blk + 1 < nblk) fetch_block(blk + 1, pre);
+		const int nt = min(DELTA_TB, cnt - blk * DELTA_TB);
+		for (int tt = 0; tt < nt; ++tt) {
+			const float* tk = cur + tt * tok_len;
+			const float4 *ks = (const float4*)(tk + part * QP), *qs = (const float4*)(tk + 4 * QP + part * QP), *gs = (const float4*)(tk + 8 * QP + part * QP);
 			float dot = 0.f;
 #pragma unroll
-			for (int i = 0; i < Q; ++i) {
-				S[i] *= gs[i];
-				dot = fmaf(S[i], ks[i], dot);
+			for (int i = 0; i < Q / 4; ++i) {
+				const float4 g4 = gs[i], k4 = ks[i];
+				S[4 * i] *= g4.x, S[4 * i + 1] *= g4.y, S[4 * i + 2] *= g4.z, S[4 * i + 3] *= g4.w;
+				dot = fmaf(S[4 * i], k4.x, dot), dot = fmaf(S[4 * i + 1], k4.y, dot), dot = fmaf(S[4 * i + 2], k4.z, dot), dot = fmaf(S[4 * i + 3], k4.w, dot);
 			}
 			dot += __shfl_xor_sync(0xffffffffu, dot, 1);
 			dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-			const float u = cur[3 * 4 * QP + V] * (cur[3 * 4 * QP + col] - dot);
+			const float u = tk[3 * 4 * QP + V] * (tk[3 * 4 * QP + col] - dot);
 			float o = 0.f;
 #pragma unroll
-			for (int i = 0; i < Q; ++i) {
-				S[i] = fmaf(ks[i], u, S[i]);
-				o = fmaf(S[i], qs[i], o);
+			for (int i = 0; i < Q / 4; ++i) {
+				const float4 k4 = ks[i], q4 = qs[i];
+				S[4 * i] = fmaf(k4.x, u, S[4 * i]), S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]), S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]), S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+				o = fmaf(S[4 * i], q4.x, o), o = fmaf(S[4 * i + 1], q4.y, o), o = fmaf(S[4 * i + 2], q4.z, o), o = fmaf(S[4 * i + 3], q4.w, o);
 			}
 			o += __shfl_xor_sync(0xffffffffu, o, 1);
 			o += __shfl_xor_sync(0xffffffffu, o, 2);
-			if (part == 0 && live) a.o[((size_t)n * a.heads + h) * V + col] = o;
+			if (part == 0 && live) a.o[((size_t)(start + blk * DELTA_TB + tt) * a.heads + h) * V + col] = o;
 		}
-		if (more) {
-#pragma unroll
-			for (int r = 0; r < 2; ++r)
-				if (tid + r * (int)blockDim.x < items) put(nxt, tid + r * blockDim.x, pre[r]);
-		}
+		if (blk + 1 < nblk) put_block(buf[(blk + 1) & 1], blk + 1, pre);
 		__syncthreads();
 	}
 	if (live) {
@@ -735,13 +782,13 @@ __global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
 		}
 }
 
-// Few tokens (decode): every weight is used once, so the kernel is a stream over W.  A CTA owns 16 weight rows, its 8 warps
+// Few tokens (decode): every weight is used once, so the kernel is a stream over W.  A CTA owns 16 weight rows, its warps (8, or 16 when the matrix has few rows)
 // take interleaved 32-wide slices of K; a lane loads 16 bytes of row g and of row g + 8 per slice straight into the A
 // fragments of two m16n8k16 MMAs (the k order inside a slice is permuted the same way for A and B, which a sum over k does
 // not see); tokens are the MMA's N.  The warps' partial tiles are added in warp order through shared memory.
-template <int NT>
-__global__ void __launch_bounds__(256) k_seq_gemm_skinny(GemmArgs a) {
-	__shared__ float red[8][16][NT * 8 + 1];
+template <int NT, int NW>
+__global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
+	__shared__ float red[NW][16][NT * 8 + 1];
 	const int z = blockIdx.z, m0 = blockIdx.x * 16, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
 	const bf16* W = a.W + (size_t)z * a.wbs;
@@ -750,17 +797,17 @@ __global__ void __launch_bounds__(256) k_seq_gemm_skinny(GemmArgs a) {
 	float acc[NT][4] = {};
 	const int nslice = (a.K + 31) / 32;
 	constexpr int U = 4; // slices requested before the first is used: 8 x 16 bytes in flight per lane
-	for (int s0 = warp; s0 < nslice; s0 += 8 * U) {
+	for (int s0 = warp; s0 < nslice; s0 += NW * U) {
 		uint4 A0[U], A1[U];
 #pragma unroll
 		for (int u = 0; u < U; ++u) {
-			const int k = (s0 + 8 * u) * 32 + 8 * t;
+			const int k = (s0 + NW * u) * 32 + 8 * t;
 			A0[u] = A1[u] = make_uint4(0, 0, 0, 0);
 			if (k < a.K) A0[u] = __ldcs((const uint4*)(w0 + k)), A1[u] = __ldcs((const uint4*)(w1 + k));
 		}
 #pragma unroll
 		for (int u = 0; u < U; ++u) {
-			const int k = (s0 + 8 * u) * 32 + 8 * t;
+			const int k = (s0 + NW * u) * 32 + 8 * t;
 			const uint32_t F0[4] = {A0[u].x, A1[u].x, A0[u].y, A1[u].y}, F1[4] = {A0[u].z, A1[u].z, A0[u].w, A1[u].w};
 #pragma unroll
 			for (int j = 0; j < NT; ++j) {
@@ -779,11 +826,11 @@ __global__ void __launch_bounds__(256) k_seq_gemm_skinny(GemmArgs a) {
 		red[warp][g + 8][j * 8 + 2 * t] = acc[j][2], red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
 	}
 	__syncthreads();
-	for (int i = tid; i < 16 * NT * 8; i += 256) {
+	for (int i = tid; i < 16 * NT * 8; i += NW * 32) {
 		const int n = i / 16, r = i % 16; // consecutive threads: consecutive weight rows of one token
 		float v = 0.f;
 #pragma unroll
-		for (int w = 0; w < 8; ++w) v += red[w][r][n];
+		for (int w = 0; w < NW; ++w) v += red[w][r][n];
 		gemm_store<bf16>(a, z, n, m0 + r, v);
 	}
 }

@@ -217,10 +217,17 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	auto al8 = [](long v) { return v % 8 == 0; };
 	if (!s.m.exact && N <= 32 && K % 8 == 0 && al8(ldx) && al8(ldw) && al8(xbs) && al8(wbs) && ((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0) {
 		const dim3 grid(cdiv(M, 16), 1, batch);
+		const bool few = (long)cdiv(M, 16) * batch < 3L * s.sms && K >= 1024; // few CTAs: twice the warps per CTA keep as many bytes in flight
 		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_SKINNY, bytes, flops, [&] {
-			if (N <= 8) k_seq_gemm_skinny<1><<<grid, 256, 0, s.stream>>>(a);
-			else if (N <= 16) k_seq_gemm_skinny<2><<<grid, 256, 0, s.stream>>>(a);
-			else k_seq_gemm_skinny<4><<<grid, 256, 0, s.stream>>>(a);
+			if (few) {
+				if (N <= 8) k_seq_gemm_skinny<1, 16><<<grid, 512, 0, s.stream>>>(a);
+				else if (N <= 16) k_seq_gemm_skinny<2, 16><<<grid, 512, 0, s.stream>>>(a);
+				else k_seq_gemm_skinny<4, 16><<<grid, 512, 0, s.stream>>>(a);
+			} else {
+				if (N <= 8) k_seq_gemm_skinny<1, 8><<<grid, 256, 0, s.stream>>>(a);
+				else if (N <= 16) k_seq_gemm_skinny<2, 8><<<grid, 256, 0, s.stream>>>(a);
+				else k_seq_gemm_skinny<4, 8><<<grid, 256, 0, s.stream>>>(a);
+			}
 		});
 		return;
 	}
@@ -298,7 +305,7 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	// few tokens over a long context: the keys of one (token, head tile) are shared out over several CTAs
 	const int live = a.skip ? std::max(1, sb.N - s.tok_on_products) : sb.N; // tokens the fused kernel really serves (the others' CTAs leave at once)
 	const int ctas = live * (a.heads / a.tile), chunks = cdiv(a.window > 0 ? std::min(longest, a.window) : longest, ATT_KC);
-	a.nsplit = ctas >= 2 * s.sms ? 1 : std::max(1, std::min({chunks / 2, 2 * s.sms / ctas, 64}));
+	a.nsplit = ctas >= 2 * s.sms ? 1 : std::max(1, std::min({chunks, 2 * s.sms / ctas, 128}));
 	if (a.nsplit > 1) {
 		const size_t need = (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2);
 		if (need > s.part_cap) {
@@ -368,13 +375,14 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		d.state = r.delta, d.o = s.f[5], d.heads = H, d.kv_heads = G, d.dim = D, d.vdim = Dv;
 		const size_t smem = ((size_t)D * Dv + 3 * D) * sizeof(float);
 		const int threads = std::max(64, cdiv(Dv, 32) * 32);
-		const size_t smem_reg = 2 * (size_t)(3 * (D + 4) + Dv + 1) * sizeof(float);
-		const int threads_reg = std::max(256, cdiv(4 * Dv, 32) * 32); // two staging rounds cover 3 D + Dv + 1 items
-		const bool reg = (D == 32 || D == 64 || D == 128) && 4 * Dv <= 512 && !getenv("CALM_B200_SEQ_DELTA_SMEM");
+		const size_t smem_reg = 2 * (size_t)DELTA_TB * (3 * (D + 16) + ((Dv + 4) & ~3)) * sizeof(float);
+		const int threads_reg = std::max(256, cdiv(4 * Dv, 32) * 32); // two staging rounds cover DELTA_TB * ((3 D + Dv) / 4 + 1) items
+		const bool reg = (D == 32 || D == 64 || D == 128) && 4 * Dv <= 512 && Dv % 4 == 0 && !getenv("CALM_B200_SEQ_DELTA_SMEM");
 		run_kernel(s, KD_DELTA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 6.0, [&] {
-			if (reg && D == 32) k_seq_delta_scan_reg<32><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
-			else if (reg && D == 64) k_seq_delta_scan_reg<64><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
-			else if (reg && D == 128) k_seq_delta_scan_reg<128><<<dim3(sb.B, H), threads_reg, smem_reg, s.stream>>>(d, sb);
+			const dim3 grid(sb.B, H);
+			if (reg && D == 32) k_seq_delta_scan_reg<32><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
+			else if (reg && D == 64) k_seq_delta_scan_reg<64><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
+			else if (reg && D == 128) k_seq_delta_scan_reg<128><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
 			else k_seq_delta_scan<<<dim3(sb.B, H), threads, smem, s.stream>>>(d, sb);
 		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
