@@ -8,6 +8,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <map>
 #include <vector>
 
 #include "seqkernels.cuh"
@@ -80,6 +81,10 @@ struct Seq {
 	bool trace = false;
 	float* trace_buf = nullptr;
 	int trace_cap = 0;
+
+	// decode steps (one token per sequence) replay a captured graph per (batch, wanted rows, key shares of every attention run)
+	bool use_graph = true;
+	std::map<std::vector<int>, std::pair<cudaGraphExec_t, int>> graphs; // -> (graph, launches in it)
 
 	bool perf = false;
 	double kind_ms[KD_COUNT] = {}, kind_bytes[KD_COUNT] = {}, kind_flops[KD_COUNT] = {};
@@ -159,7 +164,13 @@ void validate(const Seq& s) {
 	}
 }
 
+void drop_graphs(Seq& s) {
+	for (auto& kv : s.graphs) cudaGraphExecDestroy(kv.second.first);
+	s.graphs.clear();
+}
+
 void reserve_tokens(Seq& s, int N, int B, int W) {
+	if (B > s.cap_seqs || N > s.cap_tokens || W > s.cap_want) drop_graphs(s); // captured launches hold the old addresses
 	if (B > s.cap_seqs || N > s.cap_tokens) {
 		const int cn = std::max(N, s.cap_tokens), cb = std::max(B, s.cap_seqs);
 		CUDA_CHECK(cudaStreamSynchronize(s.stream));
@@ -246,6 +257,19 @@ void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, 
 	});
 }
 
+// CTAs that share the keys of one (token, head tile): few tokens over a long context
+int attn_nsplit(const Seq& s, int live_tokens, int tiles, int window, int longest) {
+	const int ctas = live_tokens * tiles, chunks = cdiv(window > 0 ? std::min(longest, window) : longest, ATT_KC);
+	return ctas >= 2 * s.sms ? 1 : std::max(1, std::min({chunks, 2 * s.sms / ctas, 128}));
+}
+void ensure_part(Seq& s, size_t need) {
+	if (need <= s.part_cap) return;
+	CUDA_CHECK(cudaStreamSynchronize(s.stream));
+	drop_graphs(s);
+	cudaFree(s.part);
+	s.part = (float*)dalloc(need * sizeof(float)), s.part_cap = need;
+}
+
 // Sequences that bring at least this many tokens to a step have their attention computed as products (bf16 mode).
 const int kAttnGemmMin = 16;
 
@@ -304,16 +328,8 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	const size_t smem = attn_smem(a.tile, a.kd);
 	// few tokens over a long context: the keys of one (token, head tile) are shared out over several CTAs
 	const int live = a.skip ? std::max(1, sb.N - s.tok_on_products) : sb.N; // tokens the fused kernel really serves (the others' CTAs leave at once)
-	const int ctas = live * (a.heads / a.tile), chunks = cdiv(a.window > 0 ? std::min(longest, a.window) : longest, ATT_KC);
-	a.nsplit = ctas >= 2 * s.sms ? 1 : std::max(1, std::min({chunks, 2 * s.sms / ctas, 128}));
-	if (a.nsplit > 1) {
-		const size_t need = (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2);
-		if (need > s.part_cap) {
-			CUDA_CHECK(cudaStreamSynchronize(s.stream));
-			cudaFree(s.part);
-			s.part = (float*)dalloc(need * sizeof(float)), s.part_cap = need;
-		}
-	}
+	a.nsplit = attn_nsplit(s, live, a.heads / a.tile, a.window, longest);
+	ensure_part(s, (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2));
 	a.part = s.part;
 	const dim3 grid(sb.N, a.heads / a.tile, a.nsplit);
 	const double bytes = kv_rows * (a.heads / a.group) * (a.kc == a.vc ? a.kd : a.kd + a.vd) * 4.0;
@@ -410,6 +426,65 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 	}
 }
 
+// every launch of one step, in order
+void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest) {
+	const SeqModel& m = s.m;
+	const int N = sb.N;
+	const bool looped = m.loop_times > 1;
+	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
+	           [&] { k_seq_embed<<<N, 128, 0, s.stream>>>(s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
+	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
+		RunState& r = s.runs[ri];
+		const SeqLayer& L = s.layers[r.layer];
+		if (r.readd) {
+			const size_t n = (size_t)N * m.width;
+			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { k_seq_add<<<cdiv(n, 256), 256, 0, s.stream>>>(s.x, s.x0, n); });
+		}
+		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
+		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows, longest);
+		else mixer_typed<bf16>(s, L, r, sb, kv_rows, longest);
+		if (s.trace)
+			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
+	}
+	if (n_want) {
+		dyt(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
+		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
+	}
+}
+
+// One decoded token per sequence: the launch list depends only on the batch size, the rows wanted and how many CTAs share the keys
+// of each attention run, so it is captured once per such key and replayed (the batch description, page table and tokens are data).
+void forward_decode_graph(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest) {
+	std::vector<int> key = {sb.N, n_want};
+	size_t part_need = 0;
+	for (const RunState& r : s.runs) {
+		const SeqLayer& L = s.layers[r.layer];
+		if (L.type == SEQ_DELTA) continue;
+		const bool lat = L.type == SEQ_LATENT;
+		const int group = lat ? L.heads : L.heads / L.kv_heads, kd = lat ? L.kv_rank : L.dim, vd = lat ? L.kv_rank : L.vdim;
+		const int ns = attn_nsplit(s, sb.N, L.heads / attn_tile(group, kd, vd), lat ? 0 : L.window, longest);
+		key.push_back(ns);
+		part_need = std::max(part_need, (size_t)sb.N * L.heads * ns * (vd + 2));
+	}
+	ensure_part(s, part_need); // no allocation inside a capture
+	auto it = s.graphs.find(key);
+	if (it == s.graphs.end()) {
+		if (s.graphs.size() > 256) drop_graphs(s);
+		const uint64_t before = g_seq_launches;
+		cudaGraph_t graph = nullptr;
+		cudaGraphExec_t exec = nullptr;
+		CUDA_CHECK(cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeThreadLocal));
+		forward(s, sb, n_want, kv_rows, longest);
+		CUDA_CHECK(cudaStreamEndCapture(s.stream, &graph));
+		CUDA_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+		CUDA_CHECK(cudaGraphDestroy(graph));
+		it = s.graphs.emplace(key, std::make_pair(exec, (int)(g_seq_launches - before))).first;
+		g_seq_launches = before;
+	}
+	CUDA_CHECK(cudaGraphLaunch(it->second.first, s.stream));
+	g_seq_launches += it->second.second;
+}
+
 } // namespace
 
 // ---------------------------------------------------------------- C ABI
@@ -441,6 +516,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	for (cudaEvent_t& e : s.ev) CUDA_CHECK(cudaEventCreate(&e));
 	for (cudaEvent_t& e : s.timer) CUDA_CHECK(cudaEventCreate(&e));
 	if (const char* e = getenv("CALM_B200_SEQ_ATTN_PRODUCTS")) s.attn_products = atoi(e) != 0;
+	if (const char* e = getenv("CALM_B200_SEQ_GRAPH")) s.use_graph = atoi(e) != 0;
 	const char* tc = getenv("CALM_B200_SEQ_TC");
 	s.tc = !s.m.exact && !(tc && atoi(tc) == 0);
 	if (s.tc) gemm_tc_setup();
@@ -502,6 +578,7 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	Seq* s = (Seq*)handle;
 	if (!s) return;
 	cudaStreamSynchronize(s->stream);
+	drop_graphs(*s);
 	for (RunState& r : s->runs) cudaFree(r.cache_a), cudaFree(r.cache_b), cudaFree(r.conv), cudaFree(r.delta);
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
@@ -601,28 +678,12 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 	sb.tok = s.d_tok, sb.tslot = s.d_tslot, sb.tpos = s.d_tpos, sb.tfirst = s.d_tfirst, sb.sstart = s.d_sstart, sb.scount = s.d_scount, sb.spos0 = s.d_spos0, sb.sslot = s.d_sslot;
 	sb.pages = s.table_dev, sb.N = N, sb.B = n_seq, sb.max_pages = s.max_pages, sb.page = m.page;
 
-	const bool looped = m.loop_times > 1;
-	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
-	           [&] { k_seq_embed<<<N, 128, 0, s.stream>>>(s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
-	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
-		RunState& r = s.runs[ri];
-		const SeqLayer& L = s.layers[r.layer];
-		if (r.readd) {
-			const size_t n = (size_t)N * m.width;
-			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { k_seq_add<<<cdiv(n, 256), 256, 0, s.stream>>>(s.x, s.x0, n); });
-		}
-		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
-		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows, longest);
-		else mixer_typed<bf16>(s, L, r, sb, kv_rows, longest);
-		if (s.trace)
-			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
-	}
+	bool decode = s.use_graph && !s.perf && !s.trace;
+	for (int b = 0; b < n_seq && decode; ++b) decode = counts[b] == 1;
+	if (decode) forward_decode_graph(s, sb, n_want, kv_rows, longest);
+	else forward(s, sb, n_want, kv_rows, longest);
 	s.last_want = n_want, s.last_tokens = N;
-	if (n_want) {
-		dyt(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
-		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
-		if (logits_host) CUDA_CHECK(cudaMemcpyAsync(logits_host, s.logits, (size_t)n_want * m.vocab * sizeof(float), cudaMemcpyDeviceToHost, s.stream));
-	}
+	if (n_want && logits_host) CUDA_CHECK(cudaMemcpyAsync(logits_host, s.logits, (size_t)n_want * m.vocab * sizeof(float), cudaMemcpyDeviceToHost, s.stream));
 	CUDA_CHECK(cudaStreamSynchronize(s.stream));
 	if (int code = gemm_tc_error()) CALM_FATAL("seq: the tensor-core product pipeline stalled (code %d)", code);
 	return 0;
