@@ -251,13 +251,22 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 					float kv[ATT_KPL];
 #pragma unroll
 					for (int i = 0; i < ATT_KPL; ++i) kv[i] = i * 32 + lane < a.kd ? kr[i * 32 + lane] : 0.f;
-					for (int r = 0; r < R; ++r) {
-						float d = 0.f;
+					for (int r0 = 0; r0 < R; r0 += 4) { // four heads' dot products advance together: independent chains and reductions
+						float dd[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-						for (int i = 0; i < ATT_KPL; ++i)
-							if (i * 32 < a.kd) d = fmaf(qs[r * a.kd + min(i * 32 + lane, a.kd - 1)], kv[i], d);
-						d = warp_sum(d);
-						if (lane == 0) sc[r * ATT_KC + j] = d * a.scale;
+						for (int i = 0; i < ATT_KPL; ++i) {
+							if (i * 32 < a.kd) {
+								const float* qp = qs + r0 * a.kd + min(i * 32 + lane, a.kd - 1);
+#pragma unroll
+								for (int u = 0; u < 4; ++u)
+									if (r0 + u < R) dd[u] = fmaf(qp[u * a.kd], kv[i], dd[u]);
+							}
+						}
+#pragma unroll
+						for (int u = 0; u < 4; ++u) dd[u] = warp_sum(dd[u]);
+#pragma unroll
+						for (int u = 0; u < 4; ++u)
+							if (r0 + u < R && lane == u) sc[(r0 + u) * ATT_KC + j] = dd[u] * a.scale;
 					}
 				} else {
 					for (int r = 0; r < R; ++r) {
