@@ -109,6 +109,22 @@ def test_each_mixer_alone(layer, dtype):
     check_all_ways(cfg, weights(cfg, 3), tokens(cfg, 37), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_align_with_nothing(dtype):
+    """Width, ranks, head sizes and vocabulary that are multiples of neither 8 nor 4: every vector path has to step aside."""
+    mlp = {"ff": 22, "kind": "dense", "limit": 0.8}
+    cfg = config([latent(heads=3, dim=10, vdim=6, kv_rank=14, q_rank=18, mlp=mlp), delta(heads=3, kv_heads=1, dim=10, vdim=7, conv=5, a_rank=3, g_rank=5, mlp=mlp),
+                  window(heads=3, kv_heads=3, dim=6, vdim=10, conv=3, size=4, mlp=mlp)], width=50, vocab=61, loop=(0, 3, 2))
+    check_all_ways(cfg, weights(cfg, 31), tokens(cfg, 45), dtype, portions=(17, 2))
+
+
+def test_latent_wider_than_the_register_tiles():
+    """A latent of more than 512 channels: keys no longer fit a lane's registers and values take the one-head-per-CTA path."""
+    cfg = config([latent(heads=2, dim=8, vdim=8, kv_rank=528, q_rank=16)])
+    check_all_ways(cfg, weights(cfg, 32), tokens(cfg, 70), "float32", portions=(40,))
+    check_all_ways(cfg, weights(cfg, 32), tokens(cfg, 70), "bfloat16", portions=(40,))
+
+
 def test_mixed_stack_with_loop_in_the_middle():
     cfg = config([window(conv=3, size=5), latent(), delta(), window(heads=4, kv_heads=4, dim=8, vdim=8, conv=4, size=9)], width=40, loop=(1, 3, 2))
     assert plain.layer_runs(cfg)[0] == [0, 1, 2, 1, 2, 3]
