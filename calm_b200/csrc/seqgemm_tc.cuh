@@ -40,6 +40,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 
 __global__ void __launch_bounds__(TG_THREADS) k_seq_gemm_tc(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmArgs a, int w3d, int x3d,
                                                              int* err) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	extern __shared__ unsigned char smem_dyn[];
 	__shared__ __align__(8) uint64_t full[TG_STAGES], empty[TG_STAGES], accum;
 	__shared__ uint32_t tmem_base_s;

@@ -51,6 +51,7 @@ __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log
 
 // x[n] = E[tok[n]] (and a second copy when a looped span re-adds the embedding)
 __global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int n = blockIdx.x;
 	const bf16* e = table + (size_t)tok[n] * width;
 	for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -61,6 +62,7 @@ __global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* t
 }
 
 __global__ void k_seq_add(float* x, const float* y, size_t n) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i < n) x[i] += y[i];
 }
@@ -68,6 +70,7 @@ __global__ void k_seq_add(float* x, const float* y, size_t n) {
 // Dynamic Tanh: out[r][i] = tanh(alpha * x[rows ? rows[r] : r][i]) * w[i] + b[i]
 template <typename AT>
 __global__ void k_seq_dyt(AT* out, const float* x, const int* rows, const bf16* w, const bf16* b, const bf16* alpha, int R, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)R * width) return;
 	const int r = (int)(i / width), c = (int)(i % width);
@@ -84,6 +87,7 @@ struct RmsSeg {
 };
 template <typename AT>
 __global__ void k_seq_latent_norm(const float* proj, int ldp, RmsSeg sq, RmsSeg sc, AT* cq, float* cache, SeqBatch sb, float eps) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
 	if (n >= sb.N) return;
@@ -105,6 +109,7 @@ __global__ void k_seq_latent_norm(const float* proj, int ldp, RmsSeg sq, RmsSeg 
 // copy `len` columns of fp32 rows into an activation matrix
 template <typename AT>
 __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int len, int N) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)N * len) return;
 	out[i] = to_act<AT>(src[(i / len) * lds + col + i % len]);
@@ -113,6 +118,7 @@ __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int
 // feed-forward unit on the stacked [gate | up] product: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1)
 template <typename AT>
 __global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)N * ff) return;
 	const size_t n = i / ff, c = i % ff;
@@ -143,6 +149,7 @@ struct ConvArgs {
 };
 // one warp per (token, head vector)
 __global__ void k_seq_conv_heads(ConvArgs a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int n = blockIdx.x;
 	int u = blockIdx.y * (blockDim.x >> 5) + warp, s = 0;
@@ -175,6 +182,7 @@ __global__ void k_seq_conv_heads(ConvArgs a, SeqBatch sb) {
 }
 // after the convolution: the state becomes the last taps-1 projected values of each sequence
 __global__ void k_seq_conv_state(float* state, const float* proj, int ldp, int taps, int channels, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int b = blockIdx.y, ch = blockIdx.x * blockDim.x + threadIdx.x;
 	if (ch >= channels) return;
 	const int T1 = taps - 1, cnt = sb.scount[b], start = sb.sstart[b];
@@ -213,6 +221,7 @@ struct AttArgs {
 };
 template <typename AT>
 __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* out, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	extern __shared__ float sm[];
 	const int n = blockIdx.x, h0 = blockIdx.y * a.tile, R = a.tile;
 	if (a.skip && a.skip[n]) return;
@@ -367,6 +376,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 // folds the shares of one (token, head) in share order: one CTA per (token, head)
 template <typename AT>
 __global__ void k_seq_attention_merge(AttArgs a, AT* out) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int n = blockIdx.x, h = blockIdx.y, pw = a.vd + 2;
 	if (a.skip && a.skip[n]) return;
 	const float* p = a.part + ((size_t)n * a.heads + h) * a.nsplit * pw;
@@ -403,6 +413,7 @@ struct AttGather {
 	int slot, k0, C, Cp;
 };
 __global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float tile[32][33];
 	const int j0 = blockIdx.x * 32, tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8 threads
 	const int dmax = max(a.kd, a.vd);
@@ -434,6 +445,7 @@ struct AttSoftmax {
 	int ldg;
 };
 __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float red[8];
 	__shared__ float bc;
 	const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x;
@@ -485,6 +497,7 @@ struct DeltaArgs {
 	int heads, kv_heads, dim, vdim;
 };
 __global__ void k_seq_delta_scan(DeltaArgs a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	extern __shared__ float sm[];
 	const int b = blockIdx.x, h = blockIdx.y, D = a.dim, V = a.vdim;
 	const int kh = h / (a.heads / a.kv_heads);
@@ -534,6 +547,7 @@ __global__ void k_seq_delta_scan(DeltaArgs a, SeqBatch sb) {
 #define DELTA_TB 4
 template <int D>
 __global__ void __launch_bounds__(512) k_seq_delta_scan_reg(DeltaArgs a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	constexpr int Q = D / 4, QP = Q + 4;
 	extern __shared__ __align__(16) float sm[];
 	const int b = blockIdx.x, h = blockIdx.y, V = a.vdim;
@@ -655,6 +669,7 @@ __global__ void __launch_bounds__(512) k_seq_delta_scan_reg(DeltaArgs a, SeqBatc
 // read-out: o / rms(o) (per head) * w * sigmoid(gate); one warp per (token, head)
 template <typename AT>
 __global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, const bf16* w, int N, int heads, int vdim, float eps) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
 	if (u >= (size_t)N * heads) return;
@@ -679,6 +694,7 @@ struct GemmArgs {
 	int N, M, K;
 	int epi;                 // EPI_F32: Y fp32; EPI_ACT: Y of the activation type; EPI_DYT_RES: Y fp32 residual += tanh(alpha acc) w + b
 	const bf16 *nw, *nb, *na;
+	int w_immutable;         // W is a model weight: it may be read before the previous kernel has finished (products of gathered keys set 0)
 };
 template <typename AT>
 __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, int n, int m, float acc) {
@@ -691,6 +707,7 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, int n, int 
 
 // exact mode: fp32 FMA, 64 x 64 tile, 16-deep steps, 256 threads with 4 x 4 outputs each
 __global__ void __launch_bounds__(256) k_seq_gemm_f32(GemmArgs a) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float Xs[16][64 + 4], Ws[16][64 + 4];
 	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
 	const float* X = (const float*)a.X + (size_t)z * a.xbs;
@@ -749,6 +766,7 @@ __device__ __forceinline__ void gemm_fill_tile(bf16 (*dst)[GB_LD], const bf16* s
 	}
 }
 __global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ __align__(16) bf16 Xs[64][GB_LD], Ws[64][GB_LD];
 	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
 	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
@@ -806,6 +824,9 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 	float acc[NT][4] = {};
 	const int nslice = (a.K + 31) / 32;
 	constexpr int U = 4; // slices requested before the first is used: 8 x 16 bytes in flight per lane
+	pdl_launch_next();
+	bool waited = false;
+	if (!a.w_immutable) pdl_wait_prev(), waited = true;
 	for (int s0 = warp; s0 < nslice; s0 += NW * U) {
 		uint4 A0[U], A1[U];
 #pragma unroll
@@ -814,6 +835,7 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 			A0[u] = A1[u] = make_uint4(0, 0, 0, 0);
 			if (k < a.K) A0[u] = __ldcs((const uint4*)(w0 + k)), A1[u] = __ldcs((const uint4*)(w1 + k));
 		}
+		if (!waited) pdl_wait_prev(), waited = true; // the first weights (immutable) are already on their way; the activations need the previous kernel
 #pragma unroll
 		for (int u = 0; u < U; ++u) {
 			const int k = (s0 + NW * u) * 32 + 8 * t;
@@ -829,6 +851,7 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 			}
 		}
 	}
+	if (!waited) pdl_wait_prev(); // a warp without a slice still must not write before the previous kernel is done
 #pragma unroll
 	for (int j = 0; j < NT; ++j) {
 		red[warp][g][j * 8 + 2 * t] = acc[j][0], red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
@@ -846,6 +869,7 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 
 // ---------------------------------------------------------------- sampling helper
 __global__ void k_seq_argmax(const float* logits, int vocab, int* out) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float bv[32];
 	__shared__ int bi[32];
 	const float* row = logits + (size_t)blockIdx.x * vocab;

@@ -84,6 +84,7 @@ struct Seq {
 
 	// decode steps (one token per sequence) replay a captured graph per (batch, wanted rows, key shares of every attention run)
 	bool use_graph = true;
+	bool pdl = true;
 	std::map<std::vector<int>, std::pair<cudaGraphExec_t, int>> graphs; // -> (graph, launches in it)
 
 	bool perf = false;
@@ -114,6 +115,19 @@ void run_kernel(Seq& s, int kind, double bytes, double flops, F&& launch) {
 		CUDA_CHECK(cudaEventElapsedTime(&ms, s.ev[0], s.ev[1]));
 		s.kind_ms[kind] += ms, s.kind_bytes[kind] += bytes, s.kind_flops[kind] += flops, ++s.kind_launches[kind];
 	}
+}
+
+// Every kernel goes out with programmatic stream serialization allowed: it may be launched while its predecessor still runs and
+// parks in pdl_enter() until that one has completed and flushed (a no-op attribute-less launch when CALM_B200_SEQ_PDL=0).
+template <typename... KArgs, typename... Args>
+void launch_k(Seq& s, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s.stream;
+	cudaLaunchAttribute at[1];
+	at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	at[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = at, cfg.numAttrs = s.pdl ? 1 : 0;
+	CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
 }
 
 size_t in_rows(const SeqLayer& L) {
@@ -213,8 +227,9 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 // ---------------------------------------------------------------- launches
 
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
-          const SeqNorm* nrm = nullptr, int kind_as = -1) {
+          const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true) {
 	GemmArgs a;
+	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
 	a.nw = nrm ? (const bf16*)nrm->w : nullptr, a.nb = nrm ? (const bf16*)nrm->b : nullptr, a.na = nrm ? (const bf16*)nrm->alpha : nullptr;
@@ -231,29 +246,29 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 		const bool few = (long)cdiv(M, 16) * batch < 3L * s.sms && K >= 1024; // few CTAs: twice the warps per CTA keep as many bytes in flight
 		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_SKINNY, bytes, flops, [&] {
 			if (few) {
-				if (N <= 8) k_seq_gemm_skinny<1, 16><<<grid, 512, 0, s.stream>>>(a);
-				else if (N <= 16) k_seq_gemm_skinny<2, 16><<<grid, 512, 0, s.stream>>>(a);
-				else k_seq_gemm_skinny<4, 16><<<grid, 512, 0, s.stream>>>(a);
+				if (N <= 8) launch_k(s, k_seq_gemm_skinny<1, 16>, grid, 512, 0, a);
+				else if (N <= 16) launch_k(s, k_seq_gemm_skinny<2, 16>, grid, 512, 0, a);
+				else launch_k(s, k_seq_gemm_skinny<4, 16>, grid, 512, 0, a);
 			} else {
-				if (N <= 8) k_seq_gemm_skinny<1, 8><<<grid, 256, 0, s.stream>>>(a);
-				else if (N <= 16) k_seq_gemm_skinny<2, 8><<<grid, 256, 0, s.stream>>>(a);
-				else k_seq_gemm_skinny<4, 8><<<grid, 256, 0, s.stream>>>(a);
+				if (N <= 8) launch_k(s, k_seq_gemm_skinny<1, 8>, grid, 256, 0, a);
+				else if (N <= 16) launch_k(s, k_seq_gemm_skinny<2, 8>, grid, 256, 0, a);
+				else launch_k(s, k_seq_gemm_skinny<4, 8>, grid, 256, 0, a);
 			}
 		});
 		return;
 	}
 	const dim3 grid(cdiv(M, 64), cdiv(N, 64), batch);
 	run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM, bytes, flops, [&] {
-		if (s.m.exact) k_seq_gemm_f32<<<grid, 256, 0, s.stream>>>(a);
-		else k_seq_gemm_bf16<<<grid, 128, 0, s.stream>>>(a);
+		if (s.m.exact) launch_k(s, k_seq_gemm_f32, grid, 256, 0, a);
+		else launch_k(s, k_seq_gemm_bf16, grid, 128, 0, a);
 	});
 }
 
 void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R) {
 	const size_t n = (size_t)R * s.m.width;
 	run_kernel(s, KD_NORM, n * (4 + act_size(s)), 0, [&] {
-		if (s.m.exact) k_seq_dyt<float><<<cdiv(n, 256), 256, 0, s.stream>>>((float*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
-		else k_seq_dyt<bf16><<<cdiv(n, 256), 256, 0, s.stream>>>((bf16*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
+		if (s.m.exact) launch_k(s, k_seq_dyt<float>, cdiv(n, 256), 256, 0, (float*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
+		else launch_k(s, k_seq_dyt<bf16>, cdiv(n, 256), 256, 0, (bf16*)out, x, rows, (const bf16*)nm.w, (const bf16*)nm.b, (const bf16*)nm.alpha, R, s.m.width);
 	});
 }
 
@@ -298,16 +313,16 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 			AttGather g;
 			g.kc = a.kc, g.vc = a.vc, g.kld = a.kld, g.vld = a.vld, g.kcol = kvh * a.kd, g.vcol = kvh * a.vd, g.kd = a.kd, g.vd = a.vd;
 			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp;
-			run_kernel(s, kind, (double)C * (a.kd + a.vd) * 6, 0, [&] { k_seq_attn_gather<<<dim3(cdiv(Cp, 32), 4), 256, 0, s.stream>>>(g, sb); });
+			run_kernel(s, kind, (double)C * (a.kd + a.vd) * 6, 0, [&] { launch_k(s, k_seq_attn_gather, dim3(cdiv(Cp, 32), 4), 256, 0, g, sb); });
 			const int h0 = kvh * a.group;
 			const bf16* q = (const bf16*)s.a3 + ((size_t)(first + t0) * a.heads + h0) * a.kd;
-			gemm(s, q, (long)a.heads * a.kd, a.kd, s.att_kb, a.kd, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd, a.group, EPI_F32, nullptr, kind);
+			gemm(s, q, (long)a.heads * a.kd, a.kd, s.att_kb, a.kd, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd, a.group, EPI_F32, nullptr, kind, false);
 			AttSoftmax sm;
 			sm.S = s.att_s, sm.P = s.att_p, sm.T = Tb, sm.C = C, sm.Cp = Cp, sm.qpos0 = q0, sm.k0 = k0, sm.window = a.window, sm.scale = a.scale;
 			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = a.gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
-			run_kernel(s, kind, (double)a.group * Tb * Cp * 6, 0, [&] { k_seq_attn_softmax<<<dim3(Tb, a.group), 256, 0, s.stream>>>(sm); });
+			run_kernel(s, kind, (double)a.group * Tb * Cp * 6, 0, [&] { launch_k(s, k_seq_attn_softmax, dim3(Tb, a.group), 256, 0, sm); });
 			gemm(s, s.att_p, Cp, (long)Tb * Cp, s.att_vt, Cp, 0, out + ((size_t)(first + t0) * a.heads + h0) * a.vd, (long)a.heads * a.vd, a.vd, Tb, a.vd, C, a.group,
-			     EPI_ACT, nullptr, kind);
+			     EPI_ACT, nullptr, kind, false);
 		}
 		t0 += Tb;
 	}
@@ -318,7 +333,7 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	bool rest = true;
 	if (!s.m.exact && s.attn_products && s.n_on_products > 0) {
 		const size_t n = (size_t)sb.N * a.heads * a.kd;
-		run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { k_seq_cast_cols<bf16><<<cdiv(n, 256), 256, 0, s.stream>>>((bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
+		run_kernel(s, KD_ELEMENT, n * 6.0, 0, [&] { launch_k(s, k_seq_cast_cols<bf16>, cdiv(n, 256), 256, 0, (bf16*)s.a3, a.q, a.heads * a.kd, 0, a.heads * a.kd, sb.N); });
 		for (int b = 0; b < sb.B; ++b)
 			if (s.hb_count[b] >= kAttnGemmMin) attention_products(s, kind, a, (bf16*)out, sb, s.hb_slot[b], s.hb_start[b], s.hb_count[b], s.hb_pos0[b]);
 		a.skip = s.d_skip;
@@ -335,13 +350,13 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	const double bytes = kv_rows * (a.heads / a.group) * (a.kc == a.vc ? a.kd : a.kd + a.vd) * 4.0;
 	const double flops = 2.0 * kv_rows * a.heads * (a.kd + a.vd);
 	run_kernel(s, kind, a.skip ? 0 : bytes, a.skip ? 0 : flops, [&] {
-		if (s.m.exact) k_seq_attention<float><<<grid, ATT_THREADS, smem, s.stream>>>(a, (float*)out, sb);
-		else k_seq_attention<bf16><<<grid, ATT_THREADS, smem, s.stream>>>(a, (bf16*)out, sb);
+		if (s.m.exact) launch_k(s, k_seq_attention<float>, grid, ATT_THREADS, smem, a, (float*)out, sb);
+		else launch_k(s, k_seq_attention<bf16>, grid, ATT_THREADS, smem, a, (bf16*)out, sb);
 	});
 	if (a.nsplit > 1)
 		run_kernel(s, kind, 0, 0, [&] {
-			if (s.m.exact) k_seq_attention_merge<float><<<dim3(sb.N, a.heads), 128, 0, s.stream>>>(a, (float*)out);
-			else k_seq_attention_merge<bf16><<<dim3(sb.N, a.heads), 128, 0, s.stream>>>(a, (bf16*)out);
+			if (s.m.exact) launch_k(s, k_seq_attention_merge<float>, dim3(sb.N, a.heads), 128, 0, a, (float*)out);
+			else launch_k(s, k_seq_attention_merge<bf16>, dim3(sb.N, a.heads), 128, 0, a, (bf16*)out);
 		});
 }
 
@@ -349,9 +364,9 @@ void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& 
 	const int units = ca.seg[0].heads + ca.seg[1].heads + ca.seg[2].heads;
 	ca.proj = s.proj, ca.ldp = (int)in_rows(L), ca.w = (const bf16*)L.conv, ca.taps = L.taps, ca.channels = conv_channels(L), ca.state = r.conv, ca.eps = s.m.eps;
 	const double bytes = (double)sb.N * ca.channels * 8;
-	run_kernel(s, KD_CONV, bytes, 0, [&] { k_seq_conv_heads<<<dim3(sb.N, cdiv(units, 4)), 128, 0, s.stream>>>(ca, sb); });
+	run_kernel(s, KD_CONV, bytes, 0, [&] { launch_k(s, k_seq_conv_heads, dim3(sb.N, cdiv(units, 4)), 128, 0, ca, sb); });
 	if (L.taps > 1)
-		run_kernel(s, KD_CONV, 0, 0, [&] { k_seq_conv_state<<<dim3(cdiv(ca.channels, 128), sb.B), 128, 0, s.stream>>>(r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb); });
+		run_kernel(s, KD_CONV, 0, 0, [&] { launch_k(s, k_seq_conv_state, dim3(cdiv(ca.channels, 128), sb.B), 128, 0, r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb); });
 }
 
 template <typename AT>
@@ -363,7 +378,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		const int H = L.heads, D = L.dim, Dv = L.vdim, Rq = L.q_rank, Rk = L.kv_rank;
 		RmsSeg sq{0, Rq, (const bf16*)L.dq_norm}, sc{Rq, Rk, (const bf16*)L.dkv_norm};
 		run_kernel(s, KD_NORM, (double)N * (Rq + Rk) * 8, 0,
-		           [&] { k_seq_latent_norm<AT><<<dim3(cdiv(N, 4), 2), 128, 0, s.stream>>>(s.proj, P, sq, sc, a1, r.cache_a, sb, s.m.eps); });
+		           [&] { launch_k(s, k_seq_latent_norm<AT>, dim3(cdiv(N, 4), 2), 128, 0, s.proj, P, sq, sc, a1, r.cache_a, sb, s.m.eps); });
 		gemm(s, a1, Rq, 0, L.w_uq, Rq, 0, a2, (long)H * D, 0, N, H * D, Rq, 1, EPI_ACT);
 		// the key up-projection moves to the query side: q'_h = W_uk,h^T q_h, so scores and values are taken on the cached latent itself
 		gemm(s, a2, (long)H * D, D, L.w_ukT, D, (long)Rk * D, s.f[0], (long)H * Rk, Rk, N, Rk, D, H, EPI_F32);
@@ -382,7 +397,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		ca.seg[2] = ConvSeg{cv, H, Dv, 1, 0, 1.f, 0, s.f[2]};
 		conv(s, L, r, ca, sb);
 		const int lr = L.a_rank + L.g_rank;
-		run_kernel(s, KD_ELEMENT, (double)N * lr * 6, 0, [&] { k_seq_cast_cols<AT><<<cdiv((long)N * lr, 256), 256, 0, s.stream>>>(a1, s.proj, P, ca1, lr, N); });
+		run_kernel(s, KD_ELEMENT, (double)N * lr * 6, 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv((long)N * lr, 256), 256, 0, a1, s.proj, P, ca1, lr, N); });
 		gemm(s, a1, lr, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_F32);
 		gemm(s, a1 + L.a_rank, lr, 0, L.w_g2, L.g_rank, 0, s.f[4], (long)H * Dv, 0, N, H * Dv, L.g_rank, 1, EPI_F32);
 		(void)cg1;
@@ -396,13 +411,13 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		const bool reg = (D == 32 || D == 64 || D == 128) && 4 * Dv <= 512 && Dv % 4 == 0 && !getenv("CALM_B200_SEQ_DELTA_SMEM");
 		run_kernel(s, KD_DELTA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 6.0, [&] {
 			const dim3 grid(sb.B, H);
-			if (reg && D == 32) k_seq_delta_scan_reg<32><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
-			else if (reg && D == 64) k_seq_delta_scan_reg<64><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
-			else if (reg && D == 128) k_seq_delta_scan_reg<128><<<grid, threads_reg, smem_reg, s.stream>>>(d, sb);
-			else k_seq_delta_scan<<<dim3(sb.B, H), threads, smem, s.stream>>>(d, sb);
+			if (reg && D == 32) launch_k(s, k_seq_delta_scan_reg<32>, grid, threads_reg, smem_reg, d, sb);
+			else if (reg && D == 64) launch_k(s, k_seq_delta_scan_reg<64>, grid, threads_reg, smem_reg, d, sb);
+			else if (reg && D == 128) launch_k(s, k_seq_delta_scan_reg<128>, grid, threads_reg, smem_reg, d, sb);
+			else launch_k(s, k_seq_delta_scan, dim3(sb.B, H), threads, smem, d, sb);
 		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
-		           [&] { k_seq_delta_out<AT><<<cdiv((long)N * H, 4), 128, 0, s.stream>>>(a2, s.f[5], s.f[4], (const bf16*)L.out_norm, N, H, Dv, s.m.eps); });
+		           [&] { launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.f[4], (const bf16*)L.out_norm, N, H, Dv, s.m.eps); });
 		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
 	} else {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
@@ -421,7 +436,7 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		dyt(s, s.hA, s.x, nullptr, L.norm2, N);
 		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
 		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
-		           [&] { k_seq_ff_act<AT><<<cdiv((long)N * L.ff, 256), 256, 0, s.stream>>>(a2, s.proj, L.ff, N, L.limit); });
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit); });
 		gemm(s, a2, L.ff, 0, L.w_down, L.ff, 0, s.x, W, 0, N, W, L.ff, 1, EPI_DYT_RES, &L.norm2b);
 	}
 }
@@ -432,13 +447,13 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
 	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
-	           [&] { k_seq_embed<<<N, 128, 0, s.stream>>>(s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
+	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
 		RunState& r = s.runs[ri];
 		const SeqLayer& L = s.layers[r.layer];
 		if (r.readd) {
 			const size_t n = (size_t)N * m.width;
-			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { k_seq_add<<<cdiv(n, 256), 256, 0, s.stream>>>(s.x, s.x0, n); });
+			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { launch_k(s, k_seq_add, cdiv(n, 256), 256, 0, s.x, s.x0, n); });
 		}
 		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
 		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows, longest);
@@ -517,6 +532,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	for (cudaEvent_t& e : s.timer) CUDA_CHECK(cudaEventCreate(&e));
 	if (const char* e = getenv("CALM_B200_SEQ_ATTN_PRODUCTS")) s.attn_products = atoi(e) != 0;
 	if (const char* e = getenv("CALM_B200_SEQ_GRAPH")) s.use_graph = atoi(e) != 0;
+	if (const char* e = getenv("CALM_B200_SEQ_PDL")) s.pdl = atoi(e) != 0;
 	const char* tc = getenv("CALM_B200_SEQ_TC");
 	s.tc = !s.m.exact && !(tc && atoi(tc) == 0);
 	if (s.tc) gemm_tc_setup();
@@ -692,7 +708,7 @@ extern "C" int calm_b200_seq_step(void* handle, int n_seq, const int* slots, con
 extern "C" void calm_b200_seq_argmax(void* handle, int* out) {
 	Seq& s = *(Seq*)handle;
 	if (!s.last_want) return;
-	k_seq_argmax<<<s.last_want, 256, 0, s.stream>>>(s.logits, s.m.vocab, s.d_argmax);
+	launch_k(s, k_seq_argmax, s.last_want, 256, 0, s.logits, s.m.vocab, s.d_argmax);
 	CUDA_CHECK(cudaGetLastError());
 	++g_seq_launches;
 	CUDA_CHECK(cudaMemcpyAsync(out, s.d_argmax, s.last_want * sizeof(int), cudaMemcpyDeviceToHost, s.stream));
