@@ -255,7 +255,7 @@ def main():
     ap.add_argument("--pos0", type=int, default=None, help="(debug) first timed position instead of the end of the context")
     ap.add_argument("--family", default="calm", choices=["calm", "vimulorn"],
                     help="vimulorn: prompt / decode throughput of the layer-list runtime at a few realistic layer sizes beside a Llama-shaped twin "
-                         "on the calm engine (one JSON line each; the default workload and its one-line contract are untouched)")
+                         "on the calm engine (one JSON line each; the default workload and its one JSON line are untouched)")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="--family vimulorn: which sizes of calm_b200/seqbench.py to run")
     ap.add_argument("--prompt", type=int, default=2048, help="--family vimulorn: prompt length")
     ap.add_argument("--batch", type=int, default=16, help="--family vimulorn: sequences decoded together")
