@@ -74,7 +74,7 @@ def plan(cfg: dict, tensors: Dict[str, torch.Tensor]) -> Tuple[dict, List[dict],
             up[m + "ukT"] = uk.reshape(H, D, Rk).transpose(1, 2).contiguous()  # per head [kv_rank, dim]: the key side folded into the query
             rec["w_ukT"] = m + "ukT"
         else:
-            G, taps = int(mx["kv_heads"]), int(mx.get("conv", 1))
+            G, taps = int(mx.get("kv_heads", H)), int(mx.get("conv", 1))
             rec.update(kv_heads=G, taps=taps)
             if kind == "channel_delta":
                 cq, cv = G * D, H * Dv
