@@ -320,3 +320,51 @@ def test_greedy_generation_through_the_scheduler():
         for k, tok in enumerate(out):  # each generated token is the plain statement's argmax given the same history
             row = lg[len(pr) + k - 1]
             assert tok == int(row.argmax()) or row.max() - row[tok] < 1e-4 * np.abs(row).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_from_a_model_folder(tmp_path, dtype):
+    """bin/trace_run end to end: a model folder written with the container writer, steps on standard input (a batch of unequal
+    prompts, decoding together while requests leave, a second batch afterwards), logits files compared with the plain statement."""
+    import json
+    import subprocess
+
+    from calm_b200 import container
+
+    cfg = config([delta(heads=2, kv_heads=2, dim=32, vdim=16, conv=2), window(heads=4, kv_heads=1, dim=16, vdim=8, conv=4, size=11, scale=0.5),
+                  latent(heads=3, dim=8, vdim=16, kv_rank=24, q_rank=16, scale=0.6), window(heads=2, kv_heads=2, dim=8, vdim=8, conv=1, size=3, mlp=None)],
+                 width=72, vocab=211, loop=(1, 3, 2), eps=1e-6)
+    t = weights(cfg, 41, sink=0.5)
+    folder, out = tmp_path / "model", tmp_path / "out"
+    folder.mkdir(), out.mkdir()
+    (folder / "config.json").write_text(json.dumps(cfg))
+    container.write_tensors(str(folder / "model.safetensors"), t)
+    reqs = {"a": tokens(cfg, 46, 1), "b": tokens(cfg, 9, 2), "c": tokens(cfg, 4, 3), "d": tokens(cfg, 30, 4), "e": tokens(cfg, 2, 5)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": reqs["a"][:40], "want": [0, 17, 39]}, {"id": "b", "tokens": reqs["b"][:6], "want": [5]},
+                                     {"id": "c", "tokens": reqs["c"][:1], "want": [0]}], "end": []}]
+    for k in range(3):
+        ent = [{"id": "a", "tokens": [reqs["a"][40 + k]], "want": [0]}, {"id": "b", "tokens": [reqs["b"][6 + k]], "want": [0] if k != 1 else []},
+               {"id": "c", "tokens": [reqs["c"][1 + k]], "want": [0]}]
+        steps.append({"step": 1 + k, "entries": ent, "end": ["b", "c"] if k == 2 else []})
+    for k in range(3):
+        steps.append({"step": 4 + k, "entries": [{"id": "a", "tokens": [reqs["a"][43 + k]], "want": [0]}], "end": ["a"] if k == 2 else []})
+    steps.append({"step": 7, "entries": [{"id": "d", "tokens": reqs["d"][:29], "want": [28]}, {"id": "e", "tokens": reqs["e"][:1], "want": []}], "end": []})
+    steps.append({"step": 8, "entries": [{"id": "d", "tokens": reqs["d"][29:], "want": [0]}, {"id": "e", "tokens": reqs["e"][1:], "want": [0]}], "end": ["d", "e"]})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out), "--max-tokens", "96"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.splitlines() if ln.startswith("done")] == ["done %d" % s["step"] for s in steps]
+    ref = {k: plain.forward(cfg, as_f64(t), v) for k, v in reqs.items()}
+    at = {k: 0 for k in reqs}
+    for s in steps:
+        rows = []
+        for e in s["entries"]:
+            rows += [ref[e["id"]][at[e["id"]] + w] for w in e["want"]]
+            at[e["id"]] += len(e["tokens"])
+        path = out / ("%d.f32" % s["step"])
+        if rows:
+            got = np.fromfile(path, "<f4").reshape(len(rows), cfg["vocab"])
+            assert rel_err(got, np.stack(rows)) < TOL[dtype]
+        else:
+            assert not path.exists()
