@@ -62,8 +62,10 @@ class Scheduler:
     def _sample(self, reqs: List[Request], n: int, logits: Optional[np.ndarray]) -> List[int]:
         if logits is None:
             return [int(t) for t in self.model.argmax(n)]
+        from . import build as cbuild
         from . import lib
 
+        cbuild.build(target="engine")  # the device sampler lives in the calm engine's library: built on first use
         out = []
         for r, row in zip(reqs, logits):
             tok, self.rng_state = lib.sample_logits(row, r.temperature, r.minp, self.rng_state)

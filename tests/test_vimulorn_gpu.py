@@ -368,3 +368,23 @@ def test_trace_replay_from_a_model_folder(tmp_path, dtype):
             assert rel_err(got, np.stack(rows)) < TOL[dtype]
         else:
             assert not path.exists()
+
+
+def test_temperature_sampling_through_the_scheduler():
+    """Temperature / min-p requests go through the library's device sampler with the scheduler's generator state: the same seed
+    gives the same tokens, every token is one the min-p rule allows under the plain statement's distribution."""
+    cfg = config([latent(), window()])
+    t = weights(cfg, 51)
+    p = as_f64(t)
+    prompts = [tokens(cfg, 6, 91), tokens(cfg, 11, 92)]
+    with vimulorn.from_tensors(cfg, t, "float32", max_tokens=128, max_seqs=2, page=8) as m:
+        a = serving.generate(m, prompts, 6, temperature=0.9, minp=0.1, seed=7)
+        b = serving.generate(m, prompts, 6, temperature=0.9, minp=0.1, seed=7)
+        c = serving.generate(m, prompts, 6, temperature=0.9, minp=0.1, seed=8)
+    assert a == b and all(len(o) == 6 for o in a) and a != c
+    for pr, out in zip(prompts, a):
+        lg = plain.forward(cfg, p, pr + out)
+        for k, tok in enumerate(out):
+            row = lg[len(pr) + k - 1] / 0.9
+            pr_tok = np.exp(row[tok] - row.max())
+            assert pr_tok >= 0.1 * (1 - 1e-3)  # min-p: at least minp times the most likely token's probability
