@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(TG_THREADS) k_seq_gemm_tc(const __grid_constan
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 	const int m0 = blockIdx.x * TG_BM, n0 = blockIdx.y * TG_BN, z = blockIdx.z;
 	const int nkb = (a.K + TG_BK - 1) / TG_BK;
+	const GemmRows gr = gemm_rows(a, z);
+	if (n0 >= gr.count) return; // a grouped product's tile past the end of its group (uniform over the CTA, before any barrier or TMEM allocation)
 	auto a_tile = [&](int s) { return smem + (size_t)s * TG_STAGE_BYTES; };
 	auto b_tile = [&](int s) { return smem + (size_t)s * TG_STAGE_BYTES + TG_BM * TG_BK * 2; };
 	if (tid == 0) {
@@ -73,7 +75,7 @@ __global__ void __launch_bounds__(TG_THREADS) k_seq_gemm_tc(const __grid_constan
 				if (w3d) tma_load_3d(a_tile(s), &tm_w, kb * TG_BK, m0, z, &full[s]);
 				else tma_load_2d(a_tile(s), &tm_w, kb * TG_BK, m0, &full[s]);
 				if (x3d) tma_load_3d(b_tile(s), &tm_x, kb * TG_BK, n0, z, &full[s]);
-				else tma_load_2d(b_tile(s), &tm_x, kb * TG_BK, n0, &full[s]);
+				else tma_load_2d(b_tile(s), &tm_x, kb * TG_BK, gr.base + n0, &full[s]); // rows past the group are other groups' (or zero fill): never stored
 			}
 		}
 	} else if (warp == 1) {
@@ -102,11 +104,11 @@ __global__ void __launch_bounds__(TG_THREADS) k_seq_gemm_tc(const __grid_constan
 			const int q4 = warp & 3; // the TMEM lane quarter this warp may read
 			const int m = m0 + q4 * 32 + lane;
 			for (int c0 = 0; c0 < TG_BN; c0 += 32) {
-				if (n0 + c0 >= a.N) break;
+				if (n0 + c0 >= gr.count) break;
 				float v[32];
 				tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + c0, v);
 #pragma unroll
-				for (int j = 0; j < 32; ++j) gemm_store<bf16>(a, z, n0 + c0 + j, m, v[j]); // lanes = consecutive weight rows: coalesced
+				for (int j = 0; j < 32; ++j) gemm_store<bf16>(a, z, gr, n0 + c0 + j, m, v[j]); // lanes = consecutive weight rows: coalesced
 			}
 		}
 		tc_fence_before();
@@ -170,7 +172,7 @@ static inline bool gemm_tc_fits(const GemmArgs& a, int batch) {
 // false: no tensor map for one of the operands, nothing was launched
 static inline bool gemm_tc_launch(const GemmArgs& a, int batch, cudaStream_t stream) {
 	const CUtensorMap* mw = tg_map(a.W, a.M, a.K, a.ldw, a.wbs, batch, TG_BM);
-	const CUtensorMap* mx = tg_map(a.X, a.N, a.K, a.ldx, a.xbs, batch, TG_BN);
+	const CUtensorMap* mx = tg_map(a.X, a.seg ? a.x_rows : a.N, a.K, a.ldx, a.xbs, batch, TG_BN);
 	if (!mw || !mx) return false;
 	const dim3 grid((a.M + TG_BM - 1) / TG_BM, (a.N + TG_BN - 1) / TG_BN, batch);
 	k_seq_gemm_tc<<<grid, TG_THREADS, TG_SMEM, stream>>>(*mw, *mx, a, a.wbs != 0 && batch > 1, a.xbs != 0 && batch > 1, g_tg.err_dev);

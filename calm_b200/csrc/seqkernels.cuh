@@ -50,12 +50,12 @@ __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log
 // ---------------------------------------------------------------- embedding, norms, small element-wise kernels
 
 // x[n] = E[tok[n]] (and a second copy when a looped span re-adds the embedding)
-__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width) {
+__global__ void k_seq_embed(float* x, float* x0, const bf16* table, const int* tok, int N, int width, float scale) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int n = blockIdx.x;
 	const bf16* e = table + (size_t)tok[n] * width;
 	for (int i = threadIdx.x; i < width; i += blockDim.x) {
-		const float v = ldf(e + i);
+		const float v = ldf(e + i) * scale;
 		x[(size_t)n * width + i] = v;
 		if (x0) x0[(size_t)n * width + i] = v;
 	}
@@ -77,6 +77,36 @@ __global__ void k_seq_dyt(AT* out, const float* x, const int* rows, const bf16* 
 	const float a = ldf(alpha);
 	const size_t src = (size_t)(rows ? rows[r] : r) * width + c;
 	out[i] = to_act<AT>(tanhf(a * x[src]) * ldf(w + c) + ldf(b + c));
+}
+
+// RMS norm of whole rows: out[r][i] = x[row][i] / sqrt(mean(x[row]^2) + eps) * (w[i] + offset); one warp per row, the row is
+// read once (up to 32 * RMS_KEEP columns stay in registers, wider rows are read a second time)
+#define RMS_KEEP 32
+template <typename AT>
+__global__ void k_seq_rms(AT* out, const float* x, const int* rows, const bf16* w, float offset, float eps, int R, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+	if (r >= R) return;
+	const float* src = x + (size_t)(rows ? rows[r] : r) * width;
+	float keep[RMS_KEEP];
+	float ss = 0.f;
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * 32 + lane;
+		keep[i] = c < width ? src[c] : 0.f;
+		ss = fmaf(keep[i], keep[i], ss);
+	}
+	for (int c = RMS_KEEP * 32 + lane; c < width; c += 32) ss = fmaf(src[c], src[c], ss);
+	ss = warp_sum(ss);
+	const float rinv = 1.f / sqrtf(ss / (float)width + eps);
+	AT* d = out + (size_t)r * width;
+#pragma unroll
+	for (int i = 0; i < RMS_KEEP; ++i) {
+		const int c = i * 32 + lane;
+		if (c < width) d[c] = to_act<AT>(keep[i] * rinv * (ldf(w + c) + offset));
+	}
+	for (int c = RMS_KEEP * 32 + lane; c < width; c += 32) d[c] = to_act<AT>(src[c] * rinv * (ldf(w + c) + offset));
 }
 
 // RMS norm with a weight over `len` columns of src rows: segment s of blockIdx.y.  Segment 0 goes to an activation
@@ -115,13 +145,19 @@ __global__ void k_seq_cast_cols(AT* out, const float* src, int lds, int col, int
 	out[i] = to_act<AT>(src[(i / len) * lds + col + i % len]);
 }
 
-// feed-forward unit on the stacked [gate | up] product: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1)
+// feed-forward unit on the stacked [gate | up] product.  mode 0: g = min(gate, L), u = clamp(up, -L, L), y = g sigmoid(1.702 g) (u + 1);
+// mode 1: y = silu(gate) up
 template <typename AT>
-__global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit) {
+__global__ void k_seq_ff_act(AT* out, const float* gu, int ff, int N, float limit, int mode) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= (size_t)N * ff) return;
 	const size_t n = i / ff, c = i % ff;
+	if (mode == 1) {
+		const float g = gu[n * 2 * ff + c];
+		out[i] = to_act<AT>(g * sigmoidf_(g) * gu[n * 2 * ff + ff + c]);
+		return;
+	}
 	const float g = fminf(gu[n * 2 * ff + c], limit);
 	const float u = fminf(fmaxf(gu[n * 2 * ff + ff + c], -limit), limit);
 	out[i] = to_act<AT>(g * sigmoidf_(1.702f * g) * (u + 1.f));
@@ -211,10 +247,11 @@ struct AttArgs {
 	int tile;         // query heads per CTA (divides group)
 	int kd, vd;
 	int window;       // <= 0: all earlier positions
+	int keep_first;   // with a window: positions below this stay visible to every later query
 	float scale;
 	const bf16* sink; // [heads] or null
 	const float* gate;
-	int ldg;          // gate[n * ldg + h]
+	int ldg, ghs, ges; // gate[n * ldg + h * ghs + d * ges]: one value per head (ghs 1, ges 0) or per output channel (ghs vd, ges 1)
 	const int* skip;  // [N] or null: 1 = this token's attention is computed by the product path (k_seq_attn_*), the CTA leaves
 	int nsplit;       // CTAs that share one (token, head tile)'s keys; > 1: partial results go to `part`, k_seq_attention_merge finishes
 	float* part;      // [N][heads][nsplit][vd + 2]: unnormalised output, running maximum, denominator
@@ -235,9 +272,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = ATT_THREADS / 32;
 	const int slot = sb.tslot[n], pos = sb.tpos[n];
 	const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+	// visible keys in order: the kept first positions the window has left behind, [0, kf), then the window [lo, pos]
+	const int kf = min(a.keep_first, lo), total = kf + pos - lo + 1;
 	// this CTA's share of the key chunks (the whole range when nsplit == 1)
-	const int nchunk = (pos - lo) / ATT_KC + 1, per = (nchunk + a.nsplit - 1) / a.nsplit;
-	const int c_begin = lo + (int)blockIdx.z * per * ATT_KC, c_end = min(pos, lo + ((int)blockIdx.z + 1) * per * ATT_KC - 1);
+	const int nchunk = (total + ATT_KC - 1) / ATT_KC, per = (nchunk + a.nsplit - 1) / a.nsplit;
+	const int c_begin = (int)blockIdx.z * per * ATT_KC, c_end = min(total - 1, ((int)blockIdx.z + 1) * per * ATT_KC - 1);
 	for (int i = tid; i < R * a.kd; i += ATT_THREADS) qs[i] = a.q[((size_t)n * a.heads + h0) * a.kd + i];
 	if (tid < R) {
 		const bool sk = a.sink && blockIdx.z == 0; // the sink counts once: in the first share
@@ -249,8 +288,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 	const bool wide = a.vd > 2 * ATT_THREADS;
 	__syncthreads();
 	for (int c0 = c_begin; c0 <= c_end; c0 += ATT_KC) {
-		const int nk = min(ATT_KC, pos - c0 + 1);
-		if (tid < ATT_KC) rows[tid] = tid < nk ? cache_row(sb, slot, c0 + tid) : 0;
+		const int nk = min(ATT_KC, total - c0);
+		if (tid < ATT_KC) rows[tid] = tid < nk ? cache_row(sb, slot, c0 + tid < kf ? c0 + tid : lo + c0 + tid - kf) : 0;
 		__syncthreads();
 		// scores: one warp per key, lanes across the key's channels; the lane's slice of the key is read once for all heads
 		for (int j = warp; j < ATT_KC; j += nwarp) {
@@ -368,7 +407,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_seq_attention(AttArgs a, AT* ou
 		const int r = head_of(k), d = col_of(k);
 		if (r < R && d < a.vd) {
 			float v = acc[k] / lrow[r];
-			if (a.gate) v *= sigmoidf_(a.gate[(size_t)n * a.ldg + h0 + r]);
+			if (a.gate) v *= sigmoidf_(a.gate[(size_t)n * a.ldg + (size_t)(h0 + r) * a.ghs + (size_t)d * a.ges]);
 			out[((size_t)n * a.heads + h0 + r) * a.vd + d] = to_act<AT>(v);
 		}
 	}
@@ -387,8 +426,8 @@ __global__ void k_seq_attention_merge(AttArgs a, AT* out) {
 		const float m = p[z * pw + a.vd];
 		if (m != -INFINITY) l += p[z * pw + a.vd + 1] * expf(m - mx);
 	}
-	const float g = (a.gate ? sigmoidf_(a.gate[(size_t)n * a.ldg + h]) : 1.f) / l;
 	for (int d = threadIdx.x; d < a.vd; d += blockDim.x) {
+		const float g = (a.gate ? sigmoidf_(a.gate[(size_t)n * a.ldg + (size_t)h * a.ghs + (size_t)d * a.ges]) : 1.f) / l;
 		float v = 0.f;
 		for (int z = 0; z < a.nsplit; ++z) {
 			const float m = p[z * pw + a.vd];
@@ -411,6 +450,7 @@ struct AttGather {
 	bf16* Kb;   // [C][kd]
 	bf16* Vt;   // [vd][Cp]
 	int slot, k0, C, Cp;
+	int kfb;    // the first kfb gathered keys are positions 0 .. kfb-1 (kept first tokens), the rest k0, k0 + 1, ...
 };
 __global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
@@ -421,7 +461,7 @@ __global__ void k_seq_attn_gather(AttGather a, SeqBatch sb) {
 		for (int r = ty; r < 32; r += 8) {
 			const int j = j0 + r, d = d0 + tx;
 			if (j < a.C) {
-				const long row = cache_row(sb, a.slot, a.k0 + j);
+				const long row = cache_row(sb, a.slot, j < a.kfb ? j : a.k0 + j - a.kfb);
 				if (d < a.kd) a.Kb[(size_t)j * a.kd + d] = __float2bfloat16_rn(a.kc[row * a.kld + a.kcol + d]);
 				tile[r][tx] = d < a.vd ? a.vc[row * a.vld + a.vcol + d] : 0.f;
 			} else tile[r][tx] = 0.f;
@@ -439,9 +479,10 @@ struct AttSoftmax {
 	bf16* P;        // same shape
 	int T, C, Cp;
 	int qpos0, k0, window;
+	int keep_first, kfb; // columns below kfb are the kept first positions 0 .. kfb-1; column j >= kfb is position k0 + j - kfb
 	float scale;
 	const bf16* sink; // already offset to the first head of the launch, or null
-	const float* gate; // gate[t * ldg + z], already offset to the first token and head, or null
+	const float* gate; // per head: gate[t * ldg + z], already offset to the first token and head, or null (per-channel gates are applied by the caller)
 	int ldg;
 };
 __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
@@ -452,11 +493,17 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	const float* srow = a.S + ((size_t)z * a.T + t) * a.Cp;
 	bf16* prow = a.P + ((size_t)z * a.T + t) * a.Cp;
 	const int qpos = a.qpos0 + t;
-	const int hi = min(a.C - 1, qpos - a.k0);                                  // last visible column
-	const int lo = a.window > 0 ? max(0, qpos - a.window + 1 - a.k0) : 0;      // first visible column
+	const int hi = min(a.C - 1, qpos - a.k0 + a.kfb); // last visible column
+	const int wlo = a.window > 0 ? qpos - a.window + 1 : 0;
+	const int lo = a.kfb > 0 || a.keep_first > a.k0 ? 0 : max(0, wlo - a.k0); // nothing is visible before this column
+	auto seen = [&](int j) { // column j's position: a kept first token, or inside the window (j <= hi is the causal bound)
+		const int p = j < a.kfb ? j : a.k0 + j - a.kfb;
+		return p >= wlo || p < a.keep_first;
+	};
 	const float sk = a.sink ? ldf(a.sink + z) : -INFINITY;
 	float mx = sk;
-	for (int j = lo + tid; j <= hi; j += 256) mx = fmaxf(mx, srow[j] * a.scale);
+	for (int j = lo + tid; j <= hi; j += 256)
+		if (seen(j)) mx = fmaxf(mx, srow[j] * a.scale);
 	mx = warp_max(mx);
 	if ((tid & 31) == 0) red[tid >> 5] = mx;
 	__syncthreads();
@@ -467,7 +514,8 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	__syncthreads();
 	mx = bc;
 	float sum = 0.f;
-	for (int j = lo + tid; j <= hi; j += 256) sum += expf(srow[j] * a.scale - mx);
+	for (int j = lo + tid; j <= hi; j += 256)
+		if (seen(j)) sum += expf(srow[j] * a.scale - mx);
 	sum = warp_sum(sum);
 	__syncthreads();
 	if ((tid & 31) == 0) red[tid >> 5] = sum;
@@ -479,7 +527,7 @@ __global__ void __launch_bounds__(256) k_seq_attn_softmax(AttSoftmax a) {
 	}
 	__syncthreads();
 	const float f = bc;
-	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi ? expf(srow[j] * a.scale - mx) * f : 0.f);
+	for (int j = tid; j < a.Cp; j += 256) prow[j] = __float2bfloat16_rn(j >= lo && j <= hi && seen(j) ? expf(srow[j] * a.scale - mx) * f : 0.f);
 }
 
 // ---------------------------------------------------------------- gated delta rule
@@ -667,8 +715,9 @@ __global__ void __launch_bounds__(512) k_seq_delta_scan_reg(DeltaArgs a, SeqBatc
 	}
 }
 // read-out: o / rms(o) (per head) * w * sigmoid(gate); one warp per (token, head)
+// (the gate goes through a sigmoid, or through SiLU when silu_gate is set; it is read at gate[token * ldg + head * vdim + i])
 template <typename AT>
-__global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, const bf16* w, int N, int heads, int vdim, float eps) {
+__global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, int ldg, const bf16* w, int N, int heads, int vdim, float eps, int silu_gate) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -678,12 +727,252 @@ __global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, cons
 	for (int i = lane; i < vdim; i += 32) ss += src[i] * src[i];
 	ss = warp_sum(ss);
 	const float r = 1.f / sqrtf(ss / (float)vdim + eps);
-	for (int i = lane; i < vdim; i += 32) out[u * vdim + i] = to_act<AT>(src[i] * r * ldf(w + i) * sigmoidf_(gate[u * vdim + i]));
+	const float* gp = gate + (u / heads) * (size_t)ldg + (u % heads) * (size_t)vdim;
+	for (int i = lane; i < vdim; i += 32) {
+		const float g = gp[i], sg = sigmoidf_(g);
+		out[u * vdim + i] = to_act<AT>(src[i] * r * ldf(w + i) * (silu_gate ? g * sg : sg));
+	}
+}
+
+// ---------------------------------------------------------------- gated linear attention
+// Per (sequence, head): S [dim][vdim] fp32;  per token  S <- diag(a) S + k v^T,  o = S^T q  with one decay per key channel,
+// a = sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau), formed here in fp32 from the raw decay projection z (+ bias).
+// q, k, v are columns of the stacked projection (row stride ldp); q is scaled by qscale.
+struct GlaArgs {
+	const float* proj;
+	int ldp, qcol, kcol, vcol;
+	const float* z;      // [N][heads*dim] raw decay projection
+	const bf16* zb;      // [heads*dim] bias or null
+	float inv_tau, qscale;
+	float* state;        // [slots][heads][dim][vdim]
+	float* o;            // [N][heads*vdim]
+	int heads, dim, vdim;
+};
+// The state sits in registers: GLA_P lanes share a value column, each holding dim / GLA_P of its rows (R per lane).  Tokens are staged
+// GLA_TB at a time into shared memory (k, scaled q, decay; v is read by the column's lanes directly), so the loop over a block's
+// tokens has no barrier inside, only the shuffles that fold a column's partial read-outs.
+#define GLA_TB 8
+template <int R, int GLA_P>
+__global__ void __launch_bounds__(256) k_seq_gla_scan(GlaArgs a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	extern __shared__ __align__(16) float sm[];
+	const int b = blockIdx.x, h = blockIdx.y, D = a.dim, V = a.vdim;
+	const int tid = threadIdx.x, part = tid % GLA_P;
+	const int v0 = blockIdx.z * (blockDim.x / GLA_P);      // value columns of this CTA
+	const int colx = v0 + tid / GLA_P;
+	const bool live = colx < V;
+	const int col = live ? colx : V - 1;                   // lanes past the last column run along on a copy of it (whole warps shuffle)
+	const int DP = R * GLA_P;                              // rows covered (>= D; rows past D hold zeros)
+	float* ks = sm;                                        // [GLA_TB][DP], row i of lane `part` at part * R + i
+	float* qs = ks + GLA_TB * DP;
+	float* gs = qs + GLA_TB * DP;
+	float S[R];
+	float* Sg = a.state + ((size_t)sb.sslot[b] * a.heads + h) * D * V;
+#pragma unroll
+	for (int i = 0; i < R; ++i) S[i] = part * R + i < D ? Sg[(size_t)(part * R + i) * V + col] : 0.f;
+	const int start = sb.sstart[b], cnt = sb.scount[b];
+	for (int t0 = 0; t0 < cnt; t0 += GLA_TB) {
+		const int nt = min(GLA_TB, cnt - t0);
+		__syncthreads();
+		for (int e = tid; e < nt * DP; e += blockDim.x) {
+			const int tt = e / DP, i = e % DP;
+			float kv = 0.f, qv = 0.f, gv = 1.f;
+			if (i < D) {
+				const float* pr = a.proj + (size_t)(start + t0 + tt) * a.ldp;
+				kv = pr[a.kcol + h * D + i], qv = pr[a.qcol + h * D + i] * a.qscale;
+				const float z = a.z[(size_t)(start + t0 + tt) * a.heads * D + h * D + i] + (a.zb ? ldf(a.zb + h * D + i) : 0.f);
+				gv = expf(-softplusf_(-z) * a.inv_tau);
+			}
+			ks[e] = kv, qs[e] = qv, gs[e] = gv;
+		}
+		__syncthreads();
+		float vv[GLA_TB];
+#pragma unroll
+		for (int tt = 0; tt < GLA_TB; ++tt) vv[tt] = tt < nt ? a.proj[(size_t)(start + t0 + tt) * a.ldp + a.vcol + h * V + col] : 0.f;
+#pragma unroll
+		for (int tt = 0; tt < GLA_TB; ++tt) {
+			if (tt < nt) {
+				const float *kp = ks + tt * DP + part * R, *qp = qs + tt * DP + part * R, *gp = gs + tt * DP + part * R;
+				float o = 0.f;
+#pragma unroll
+				for (int i = 0; i < R; ++i) {
+					S[i] = fmaf(gp[i], S[i], kp[i] * vv[tt]);
+					o = fmaf(S[i], qp[i], o);
+				}
+#pragma unroll
+				for (int w = 1; w < GLA_P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+				if (part == 0 && live) a.o[((size_t)(start + t0 + tt) * a.heads + h) * V + col] = o;
+			}
+		}
+	}
+	if (live) {
+#pragma unroll
+		for (int i = 0; i < R; ++i)
+			if (part * R + i < D) Sg[(size_t)(part * R + i) * V + col] = S[i];
+	}
+}
+
+// ---------------------------------------------------------------- query / key preparation of grouped-query attention
+// One CTA per token, on the stacked (biased) projection [q | k | v | ...]: an RMS norm over the WHOLE query projection and one over
+// the whole key projection (all heads at once, weights qw / kw; null: no norm), then the first rot_dims channels of every head turn
+// by the token's position (channel i with channel i + rot_dims/2, angle = position * freq[i], cos and sin times `mag`); queries go
+// to an activation-independent fp32 matrix, keys and values to their cache rows.  Angles are formed in double: a position in the
+// thousands times a frequency near one leaves fp32 with too few fraction bits.
+struct QkArgs {
+	const float* proj;
+	int ldp;
+	int heads, kv_heads, dim, vdim;
+	const bf16 *qw, *kw;
+	float eps;
+	int rot_dims;
+	const double* freq; // [rot_dims / 2]
+	float mag;
+	float* q;           // [N][heads*dim]
+	float* kc;          // cache rows [kv_heads*dim]
+	float* vc;          // cache rows [kv_heads*vdim]
+};
+__global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	extern __shared__ float cs[]; // [rot_dims/2] cos, [rot_dims/2] sin
+	__shared__ float red[2][8];
+	const int n = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	const int Q = a.heads * a.dim, K = a.kv_heads * a.dim, Vn = a.kv_heads * a.vdim, half = a.rot_dims / 2;
+	const float* pr = a.proj + (size_t)n * a.ldp;
+	const int pos = sb.tpos[n];
+	const long row = cache_row(sb, sb.tslot[n], pos);
+	for (int i = tid; i < half; i += blockDim.x) {
+		double s, c;
+		sincos((double)pos * a.freq[i], &s, &c);
+		cs[i] = (float)c * a.mag, cs[half + i] = (float)s * a.mag;
+	}
+	float sq = 0.f, sk = 0.f;
+	if (a.qw) {
+		for (int i = tid; i < Q; i += blockDim.x) sq = fmaf(pr[i], pr[i], sq);
+		for (int i = tid; i < K; i += blockDim.x) sk = fmaf(pr[Q + i], pr[Q + i], sk);
+		sq = warp_sum(sq), sk = warp_sum(sk);
+		if (lane == 0) red[0][warp] = sq, red[1][warp] = sk;
+	}
+	__syncthreads();
+	float rq = 1.f, rk = 1.f;
+	if (a.qw) {
+		sq = sk = 0.f;
+		for (int w = 0; w < (int)(blockDim.x >> 5); ++w) sq += red[0][w], sk += red[1][w];
+		rq = 1.f / sqrtf(sq / (float)Q + a.eps), rk = 1.f / sqrtf(sk / (float)K + a.eps);
+	}
+	float* kd = a.kc + row * K;
+	for (int e = tid; e < Q + K; e += blockDim.x) {
+		const bool isq = e < Q;
+		const int c = isq ? e : e - Q, d = c % a.dim;
+		const bf16* w = isq ? a.qw : a.kw;
+		const float r = isq ? rq : rk;
+		const float* src = pr + (isq ? 0 : Q);
+		float v = src[c] * r * (w ? ldf(w + c) : 1.f);
+		if (d < a.rot_dims) {
+			const int i = d < half ? d : d - half, o = d < half ? c + half : c - half;
+			const float other = src[o] * r * (w ? ldf(w + o) : 1.f);
+			v = d < half ? v * cs[i] - other * cs[half + i] : v * cs[i] + other * cs[half + i];
+		}
+		if (isq) a.q[(size_t)n * Q + c] = v;
+		else kd[c] = v;
+	}
+	float* vd = a.vc + row * Vn;
+	for (int i = tid; i < Vn; i += blockDim.x) vd[i] = pr[Q + K + i];
+}
+
+// ---------------------------------------------------------------- routed experts
+// Router: per token the `top` largest logits (lowest index wins a tie), softmax over those only.  One warp per token.
+__global__ void k_seq_moe_route(const float* logits, int experts, int top, int N, int* sel, float* wt) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+	if (n >= N) return;
+	const float* z = logits + (size_t)n * experts;
+	float first = 0.f, sum = 0.f;
+	for (int k = 0; k < top; ++k) {
+		float bv = -INFINITY;
+		int bi = 0x7fffffff;
+		for (int e = lane; e < experts; e += 32) {
+			bool taken = false;
+			for (int j = 0; j < k; ++j) taken |= sel[(size_t)n * top + j] == e; // written by lane 0 below, visible after the warp barrier
+			if (!taken && z[e] > bv) bv = z[e], bi = e;
+		}
+		for (int o = 16; o > 0; o >>= 1) {
+			const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+			const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+			if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+		}
+		if (k == 0) first = bv;
+		const float p = expf(bv - first); // the first chosen logit is the largest: the softmax's maximum
+		sum += p;
+		if (lane == 0) sel[(size_t)n * top + k] = bi, wt[(size_t)n * top + k] = p;
+		__syncwarp();
+	}
+	for (int k = lane; k < top; k += 32) wt[(size_t)n * top + k] /= sum;
+}
+// Groups the (token, choice) pairs by expert, pairs of one expert in token order: one CTA per expert counts the pairs of lower
+// experts (its group's first row) and places its own.  seg[e] .. seg[e+1] are expert e's rows, perm[row] = pair, inv[pair] = row.
+__global__ void __launch_bounds__(256) k_seq_moe_group(const int* sel, int pairs, int experts, int* seg, int* perm, int* inv) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	__shared__ int wsum[8], base_s, run_s;
+	const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	int below = 0;
+	for (int i = tid; i < pairs; i += 256) below += sel[i] < e;
+	for (int o = 16; o > 0; o >>= 1) below += __shfl_xor_sync(0xffffffffu, below, o);
+	if (lane == 0) wsum[warp] = below;
+	__syncthreads();
+	if (tid == 0) {
+		int s = 0;
+		for (int w = 0; w < 8; ++w) s += wsum[w];
+		base_s = s, run_s = 0;
+		seg[e] = s;
+		if (e == experts - 1) seg[experts] = pairs;
+	}
+	__syncthreads();
+	const int base = base_s;
+	for (int i0 = 0; i0 < pairs; i0 += 256) {
+		const int i = i0 + tid;
+		const bool mine = i < pairs && sel[i] == e;
+		const unsigned bal = __ballot_sync(0xffffffffu, mine);
+		__syncthreads(); // the previous round's readers of wsum / run_s are done
+		if (lane == 0) wsum[warp] = __popc(bal);
+		__syncthreads();
+		int before = run_s;
+		for (int w = 0; w < warp; ++w) before += wsum[w];
+		if (mine) {
+			const int r = base + before + __popc(bal & ((1u << lane) - 1));
+			perm[r] = i, inv[i] = r;
+		}
+		__syncthreads();
+		if (tid == 0) {
+			int s = run_s;
+			for (int w = 0; w < 8; ++w) s += wsum[w];
+			run_s = s;
+		}
+	}
+}
+// rows of the grouped activation matrix: Xp[row] = h[perm[row] / top]
+template <typename AT>
+__global__ void k_seq_moe_gather(AT* xp, const AT* h, const int* perm, int top, int pairs, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)pairs * width) return;
+	const size_t r = i / width, c = i % width;
+	xp[i] = h[(size_t)(perm[r] / top) * width + c];
+}
+// x[n] += (res ? res[n] : 0) + sum_k wt[n][k] * y[inv[n * top + k]]   (choices in order of rank)
+__global__ void k_seq_moe_combine(float* x, const float* res, const float* y, const int* inv, const float* wt, int top, int N, int width) {
+	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= (size_t)N * width) return;
+	const size_t n = i / width, c = i % width;
+	float s = 0.f;
+	for (int k = 0; k < top; ++k) s = fmaf(wt[n * top + k], y[(size_t)inv[n * top + k] * width + c], s);
+	x[i] += res ? res[i] + s : s;
 }
 
 // ---------------------------------------------------------------- products  Y[n][m] = sum_k X[n][k] W[m][k]
 // blockIdx.z = batch (per-head products): X, W, Y advance by xbs, wbs, ybs elements.
-enum { EPI_F32 = 0, EPI_ACT = 1, EPI_DYT_RES = 2 };
+enum { EPI_F32 = 0, EPI_ACT = 1, EPI_DYT_RES = 2, EPI_RES = 3, EPI_ACT_RELU2 = 4 };
 struct GemmArgs {
 	const void* X;
 	long ldx, xbs;
@@ -692,17 +981,40 @@ struct GemmArgs {
 	void* Y;
 	long ldy, ybs;
 	int N, M, K;
-	int epi;                 // EPI_F32: Y fp32; EPI_ACT: Y of the activation type; EPI_DYT_RES: Y fp32 residual += tanh(alpha acc) w + b
+	int epi;                 // EPI_F32: Y fp32; EPI_ACT: Y of the activation type; EPI_DYT_RES: Y fp32 residual += tanh(alpha acc) w + b;
+	                         // EPI_RES: Y fp32 residual += (res ? res : 0) + acc; EPI_ACT_RELU2: Y of the activation type = relu(acc)^2
 	const bf16 *nw, *nb, *na;
 	int w_immutable;         // W is a model weight: it may be read before the previous kernel has finished (products of gathered keys set 0)
+	const bf16* bias;        // [batch][M] or null: added to the accumulator first
+	const float* res;        // EPI_RES: a second addend laid out like Y, or null
+	const float* gate;       // EPI_ACT: the output is multiplied by sigmoid(gate[z * gbs + n * ldgate + m]); null: none
+	long ldgate, gbs;
+	const int* seg;          // grouped products: batch z owns rows [seg[z], seg[z+1]) of X and Y (xbs = ybs = 0), N bounds one group; null: none
+	int x_rows;              // grouped products: rows of X and Y over all groups
 };
+// rows of batch z: first row and count
+struct GemmRows {
+	int base, count;
+};
+__device__ __forceinline__ GemmRows gemm_rows(const GemmArgs& a, int z) {
+	if (!a.seg) return GemmRows{0, a.N};
+	const int b = a.seg[z];
+	return GemmRows{b, a.seg[z + 1] - b};
+}
 template <typename AT>
-__device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, int n, int m, float acc) {
-	if (n >= a.N || m >= a.M) return;
-	const size_t o = (size_t)z * a.ybs + (size_t)n * a.ldy + m;
+__device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmRows& gr, int n, int m, float acc) {
+	if (n >= gr.count || m >= a.M) return;
+	const size_t o = (size_t)z * a.ybs + (size_t)(gr.base + n) * a.ldy + m;
+	if (a.bias) acc += ldf(a.bias + (size_t)z * a.M + m);
 	if (a.epi == EPI_F32) ((float*)a.Y)[o] = acc;
-	else if (a.epi == EPI_ACT) ((AT*)a.Y)[o] = to_act<AT>(acc);
-	else ((float*)a.Y)[o] += tanhf(ldf(a.na) * acc) * ldf(a.nw + m) + ldf(a.nb + m);
+	else if (a.epi == EPI_ACT) {
+		if (a.gate) acc *= sigmoidf_(a.gate[(size_t)z * a.gbs + (size_t)(gr.base + n) * a.ldgate + m]);
+		((AT*)a.Y)[o] = to_act<AT>(acc);
+	} else if (a.epi == EPI_RES) ((float*)a.Y)[o] += a.res ? a.res[o] + acc : acc;
+	else if (a.epi == EPI_ACT_RELU2) {
+		const float r = fmaxf(acc, 0.f);
+		((AT*)a.Y)[o] = to_act<AT>(r * r);
+	} else ((float*)a.Y)[o] += tanhf(ldf(a.na) * acc) * ldf(a.nw + m) + ldf(a.nb + m);
 }
 
 // exact mode: fp32 FMA, 64 x 64 tile, 16-deep steps, 256 threads with 4 x 4 outputs each
@@ -710,14 +1022,16 @@ __global__ void __launch_bounds__(256) k_seq_gemm_f32(GemmArgs a) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ float Xs[16][64 + 4], Ws[16][64 + 4];
 	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
-	const float* X = (const float*)a.X + (size_t)z * a.xbs;
+	const GemmRows gr = gemm_rows(a, z);
+	if (n0 >= gr.count) return;
+	const float* X = (const float*)a.X + (size_t)z * a.xbs + (size_t)gr.base * a.ldx;
 	const bf16* W = a.W + (size_t)z * a.wbs;
 	const int tn = (tid / 16) * 4, tm = (tid % 16) * 4;
 	float acc[4][4] = {};
 	for (int k0 = 0; k0 < a.K; k0 += 16) {
 		for (int i = tid; i < 64 * 16; i += 256) {
 			const int r = i / 16, k = i % 16;
-			Xs[k][r] = (n0 + r < a.N && k0 + k < a.K) ? X[(size_t)(n0 + r) * a.ldx + k0 + k] : 0.f;
+			Xs[k][r] = (n0 + r < gr.count && k0 + k < a.K) ? X[(size_t)(n0 + r) * a.ldx + k0 + k] : 0.f;
 			Ws[k][r] = (m0 + r < a.M && k0 + k < a.K) ? ldf(W + (size_t)(m0 + r) * a.ldw + k0 + k) : 0.f;
 		}
 		__syncthreads();
@@ -736,7 +1050,7 @@ __global__ void __launch_bounds__(256) k_seq_gemm_f32(GemmArgs a) {
 #pragma unroll
 	for (int i = 0; i < 4; ++i)
 #pragma unroll
-		for (int j = 0; j < 4; ++j) gemm_store<float>(a, z, n0 + tn + i, m0 + tm + j, acc[i][j]);
+		for (int j = 0; j < 4; ++j) gemm_store<float>(a, z, gr, n0 + tn + i, m0 + tm + j, acc[i][j]);
 }
 
 // bf16 x bf16 -> fp32 on the tensor cores for ANY shape (edges are zero-filled in shared memory): 64 tokens x 64 rows per
@@ -769,13 +1083,15 @@ __global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	__shared__ __align__(16) bf16 Xs[64][GB_LD], Ws[64][GB_LD];
 	const int z = blockIdx.z, n0 = blockIdx.y * 64, m0 = blockIdx.x * 64, tid = threadIdx.x;
-	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
+	const GemmRows gr = gemm_rows(a, z);
+	if (n0 >= gr.count) return;
+	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs + (size_t)gr.base * a.ldx;
 	const bf16* W = a.W + (size_t)z * a.wbs;
 	const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 	const int wn = (warp >> 1) * 32, wm = (warp & 1) * 32;
 	float acc[2][4][4] = {};
 	for (int k0 = 0; k0 < a.K; k0 += 32) {
-		gemm_fill_tile(Xs, X, a.ldx, n0, a.N, k0, a.K, tid);
+		gemm_fill_tile(Xs, X, a.ldx, n0, gr.count, k0, a.K, tid);
 		gemm_fill_tile(Ws, W, a.ldw, m0, a.M, k0, a.K, tid);
 		__syncthreads();
 #pragma unroll
@@ -804,8 +1120,8 @@ __global__ void __launch_bounds__(128) k_seq_gemm_bf16(GemmArgs a) {
 #pragma unroll
 		for (int j = 0; j < 4; ++j) {
 			const int n = n0 + wn + i * 16 + g, m = m0 + wm + j * 8 + 2 * t;
-			gemm_store<bf16>(a, z, n, m, acc[i][j][0]), gemm_store<bf16>(a, z, n, m + 1, acc[i][j][1]);
-			gemm_store<bf16>(a, z, n + 8, m, acc[i][j][2]), gemm_store<bf16>(a, z, n + 8, m + 1, acc[i][j][3]);
+			gemm_store<bf16>(a, z, gr, n, m, acc[i][j][0]), gemm_store<bf16>(a, z, gr, n, m + 1, acc[i][j][1]);
+			gemm_store<bf16>(a, z, gr, n + 8, m, acc[i][j][2]), gemm_store<bf16>(a, z, gr, n + 8, m + 1, acc[i][j][3]);
 		}
 }
 
@@ -817,16 +1133,22 @@ template <int NT, int NW>
 __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 	__shared__ float red[NW][16][NT * 8 + 1];
 	const int z = blockIdx.z, m0 = blockIdx.x * 16, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs;
+	bool waited = false;
+	pdl_launch_next();
+	GemmRows gr{0, a.N};
+	if (a.seg) { // the groups come from the previous kernel: a group without rows leaves before it touches its weights
+		pdl_wait_prev(), waited = true;
+		gr = gemm_rows(a, z);
+		if (gr.count == 0) return;
+	}
+	const bf16* X = (const bf16*)a.X + (size_t)z * a.xbs + (size_t)gr.base * a.ldx;
 	const bf16* W = a.W + (size_t)z * a.wbs;
 	const bf16* w0 = W + (size_t)min(m0 + g, a.M - 1) * a.ldw;
 	const bf16* w1 = W + (size_t)min(m0 + g + 8, a.M - 1) * a.ldw;
 	float acc[NT][4] = {};
 	const int nslice = (a.K + 31) / 32;
 	constexpr int U = 4; // slices requested before the first is used: 8 x 16 bytes in flight per lane
-	pdl_launch_next();
-	bool waited = false;
-	if (!a.w_immutable) pdl_wait_prev(), waited = true;
+	if (!a.w_immutable && !waited) pdl_wait_prev(), waited = true;
 	for (int s0 = warp; s0 < nslice; s0 += NW * U) {
 		uint4 A0[U], A1[U];
 #pragma unroll
@@ -844,7 +1166,7 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 			for (int j = 0; j < NT; ++j) {
 				uint4 B = make_uint4(0, 0, 0, 0);
 				const int n = j * 8 + g;
-				if (n < a.N && k < a.K) B = *(const uint4*)(X + (size_t)n * a.ldx + k);
+				if (n < gr.count && k < a.K) B = *(const uint4*)(X + (size_t)n * a.ldx + k);
 				const uint32_t B0[2] = {B.x, B.y}, B1[2] = {B.z, B.w};
 				mma_bf16_16816(acc[j], F0, B0);
 				mma_bf16_16816(acc[j], F1, B1);
@@ -863,7 +1185,7 @@ __global__ void __launch_bounds__(NW * 32) k_seq_gemm_skinny(GemmArgs a) {
 		float v = 0.f;
 #pragma unroll
 		for (int w = 0; w < NW; ++w) v += red[w][r][n];
-		gemm_store<bf16>(a, z, n, m0 + r, v);
+		gemm_store<bf16>(a, z, gr, n, m0 + r, v);
 	}
 }
 

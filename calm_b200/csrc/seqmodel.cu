@@ -18,17 +18,18 @@ namespace {
 
 uint64_t g_seq_launches = 0;
 
-enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_GEMM_SKINNY, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_COUNT };
-const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "gemm_skinny", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise"};
+enum Kind { KD_EMBED, KD_NORM, KD_GEMM, KD_GEMM_TC, KD_GEMM_SKINNY, KD_CONV, KD_ATTN_LATENT, KD_ATTN_WINDOW, KD_DELTA, KD_ELEMENT, KD_QK, KD_GLA, KD_ROUTE, KD_COUNT };
+const char* const kKindNames[KD_COUNT] = {"embed", "norm", "gemm", "gemm_tcgen05", "gemm_skinny", "conv", "attention_latent", "attention_window", "delta_scan", "elementwise",
+                                          "qk_prep", "gla_scan", "moe_route"};
 
 // what one run of a layer owns (a looped layer has one of these per pass)
 struct RunState {
 	int layer = 0;
 	bool readd = false;      // the embedding output is added to the stream right before this run
-	float* cache_a = nullptr; // SEQ_LATENT: latent rows; SEQ_WINDOW: key rows
-	float* cache_b = nullptr; // SEQ_WINDOW: value rows
+	float* cache_a = nullptr; // SEQ_LATENT: latent rows; SEQ_WINDOW / SEQ_GQA: key rows
+	float* cache_b = nullptr; // SEQ_WINDOW / SEQ_GQA: value rows
 	float* conv = nullptr;    // [slots][taps-1][channels]
-	float* delta = nullptr;   // [slots][heads][dim][vdim]
+	float* delta = nullptr;   // SEQ_DELTA / SEQ_GLA: the recurrent state [slots][heads][dim][vdim]
 	size_t conv_per_slot = 0, delta_per_slot = 0;
 };
 
@@ -42,6 +43,8 @@ struct Seq {
 	SeqModel m;
 	std::vector<SeqLayer> layers;
 	std::vector<RunState> runs;
+	std::vector<double*> rot_freq; // per layer: angle step of every rotated pair (SEQ_GQA), device
+	std::vector<float> rot_mag;    // per layer: factor on cos and sin
 	cudaStream_t stream = nullptr;
 	int sms = 0;
 	bool tc = false; // tcgen05 products available (bf16 mode)
@@ -61,6 +64,13 @@ struct Seq {
 
 	// workspace for cap_tokens tokens
 	float *x = nullptr, *x0 = nullptr, *proj = nullptr, *f[6] = {};
+	float* mo = nullptr;                              // parallel blocks: the mixer's output until the feed-forward's is added with it
+	// routed experts: choices and weights per token, groups, and the grouped activations of max_top choices per token
+	int max_top = 0, max_experts = 0;
+	size_t w_moe_ff = 0;
+	int *moe_sel = nullptr, *moe_perm = nullptr, *moe_inv = nullptr, *moe_seg = nullptr;
+	float *moe_wt = nullptr, *moe_y = nullptr, *moe_d = nullptr;
+	void *moe_x = nullptr, *moe_a = nullptr;
 	void *hA = nullptr, *a1 = nullptr, *a2 = nullptr; // activation type (float or bf16)
 	size_t w_proj = 0, w_f = 0, w_a = 0;              // widths (elements per token)
 	// prompt attention as products: gathered keys / transposed values of one key head, scores and probabilities
@@ -134,6 +144,8 @@ size_t in_rows(const SeqLayer& L) {
 	switch (L.type) {
 	case SEQ_LATENT: return (size_t)L.q_rank + L.kv_rank + L.heads;
 	case SEQ_DELTA: return (size_t)2 * L.kv_heads * L.dim + (size_t)L.heads * L.vdim + L.heads + L.a_rank + L.g_rank;
+	case SEQ_GQA: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim + (size_t)L.heads * L.vdim;
+	case SEQ_GLA: return (size_t)2 * L.heads * L.dim + (size_t)2 * L.heads * L.vdim + L.a_rank;
 	default: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim;
 	}
 }
@@ -174,8 +186,30 @@ void validate(const Seq& s) {
 				if (((size_t)L.dim * L.vdim + 3 * (size_t)L.dim) * sizeof(float) > 227 * 1024) CALM_FATAL("seq: layer %d: a %d x %d state does not fit shared memory", i, L.dim, L.vdim);
 				if (L.a_rank < 1 || L.g_rank < 1) CALM_FATAL("seq: layer %d: decay and gate ranks must be positive", i);
 			} else if (cdiv(L.vdim, ATT_THREADS) > ATT_MAXI) CALM_FATAL("seq: layer %d: vdim too large", i);
+		} else if (L.type == SEQ_GQA) {
+			if (L.kv_heads < 1 || L.heads % L.kv_heads) CALM_FATAL("seq: layer %d: heads must be a multiple of kv_heads", i);
+			if (cdiv(L.vdim, ATT_THREADS) > ATT_MAXI) CALM_FATAL("seq: layer %d: vdim too large", i);
+			if (L.rot_dims < 0 || L.rot_dims > L.dim || L.rot_dims % 2) CALM_FATAL("seq: layer %d: rot_dims must be even and at most dim", i);
+			if (L.rot_dims > 0 && !(L.rot_base > 0.f)) CALM_FATAL("seq: layer %d: rot_base must be positive", i);
+			if ((L.q_norm == nullptr) != (L.k_norm == nullptr)) CALM_FATAL("seq: layer %d: query and key norm come together", i);
+			if (L.keep_first < 0) CALM_FATAL("seq: layer %d: keep_first is negative", i);
+		} else if (L.type == SEQ_GLA) {
+			if (L.dim > 256) CALM_FATAL("seq: layer %d: a gated-linear-attention head holds at most 256 key channels", i);
+			if (L.a_rank < 1) CALM_FATAL("seq: layer %d: the decay rank must be positive", i);
+			if (!(L.tau > 0.f)) CALM_FATAL("seq: layer %d: tau must be positive", i);
 		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
+		if (L.ff > 0) {
+			if (L.ff_kind < SEQ_FF_CLAMPED || L.ff_kind > SEQ_FF_MOE) CALM_FATAL("seq: layer %d: unknown feed-forward kind %d", i, L.ff_kind);
+			if (L.ff_kind == SEQ_FF_MOE) {
+				if (L.experts < 1 || L.top < 1 || L.top > L.experts) CALM_FATAL("seq: layer %d: 1 <= top <= experts", i);
+				if (m.block != SEQ_BLOCK_PARALLEL) CALM_FATAL("seq: layer %d: routed experts are served in parallel blocks only", i);
+			}
+		}
 	}
+	if (m.norm_kind != SEQ_NORM_DYT && m.norm_kind != SEQ_NORM_RMS) CALM_FATAL("seq: unknown norm kind %d", m.norm_kind);
+	if (m.block != SEQ_BLOCK_SERIAL && m.block != SEQ_BLOCK_PARALLEL) CALM_FATAL("seq: unknown block form %d", m.block);
+	if (m.block == SEQ_BLOCK_SERIAL && m.norm_kind != SEQ_NORM_DYT)
+		CALM_FATAL("seq: serial blocks fold their second norm into the product before it, which only a norm without row statistics (Dynamic Tanh) allows");
 }
 
 void drop_graphs(Seq& s) {
@@ -205,8 +239,20 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 	}
 	if (N > s.cap_tokens) {
 		const size_t cn = N;
-		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2), cudaFree(s.a3);
+		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2), cudaFree(s.a3), cudaFree(s.mo);
 		for (float*& p : s.f) cudaFree(p);
+		if (s.m.block == SEQ_BLOCK_PARALLEL) s.mo = (float*)dalloc(cn * s.m.width * sizeof(float));
+		if (s.max_top > 0) {
+			cudaFree(s.moe_sel), cudaFree(s.moe_wt), cudaFree(s.moe_y), cudaFree(s.moe_d), cudaFree(s.moe_x), cudaFree(s.moe_a);
+			const size_t pairs = cn * s.max_top;
+			s.moe_sel = (int*)dalloc((3 * pairs + s.max_experts + 1) * sizeof(int));
+			s.moe_perm = s.moe_sel + pairs, s.moe_inv = s.moe_perm + pairs, s.moe_seg = s.moe_inv + pairs;
+			s.moe_wt = (float*)dalloc(pairs * sizeof(float));
+			s.moe_y = (float*)dalloc(pairs * 2 * s.w_moe_ff * sizeof(float));
+			s.moe_d = (float*)dalloc(pairs * s.m.width * sizeof(float));
+			s.moe_x = dalloc(pairs * s.m.width * act_size(s));
+			s.moe_a = dalloc(pairs * s.w_moe_ff * act_size(s));
+		}
 		s.x = (float*)dalloc(cn * s.m.width * sizeof(float));
 		s.x0 = (float*)dalloc(cn * s.m.width * sizeof(float));
 		s.proj = (float*)dalloc(cn * s.w_proj * sizeof(float));
@@ -226,15 +272,29 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 
 // ---------------------------------------------------------------- launches
 
+// what a product's epilogue may take besides the accumulator
+struct GemmExtra {
+	const void* bias = nullptr;  // bf16 [batch][M]
+	const float* res = nullptr;  // EPI_RES: second addend
+	const float* gate = nullptr; // EPI_ACT: sigmoid gate
+	long ldgate = 0, gbs = 0;
+	const int* seg = nullptr;    // grouped product: rows of batch z
+	int x_rows = 0;              // grouped product: rows of X / Y over all groups
+};
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
-          const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true) {
+          const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true, const GemmExtra* ex = nullptr) {
 	GemmArgs a;
+	const GemmExtra none;
+	if (!ex) ex = &none;
+	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
 	a.nw = nrm ? (const bf16*)nrm->w : nullptr, a.nb = nrm ? (const bf16*)nrm->b : nullptr, a.na = nrm ? (const bf16*)nrm->alpha : nullptr;
-	const double flops = 2.0 * N * M * K * batch;
-	const double bytes = ((double)M * K * 2 + (double)N * K * act_size(s) + (double)N * M * 4) * batch;
+	// a grouped product does the work of its x_rows rows, and reads at most that many groups' weights
+	const double rows = ex->seg ? (double)ex->x_rows : (double)N * batch, mats = ex->seg ? std::min((double)batch, rows) : (double)batch;
+	const double flops = 2.0 * rows * M * K;
+	const double bytes = mats * M * K * 2 + rows * K * act_size(s) + rows * M * 4;
 	if (s.tc && gemm_tc_fits(a, batch)) {
 		bool launched = false;
 		run_kernel(s, kind_as >= 0 ? kind_as : KD_GEMM_TC, bytes, flops, [&] { launched = gemm_tc_launch(a, batch, s.stream); });
@@ -264,6 +324,16 @@ void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, lo
 	});
 }
 
+void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R);
+// the model's norm on whole rows of the residual stream
+void norm(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R) {
+	if (s.m.norm_kind == SEQ_NORM_DYT) return dyt(s, out, x, rows, nm, R);
+	const int W = s.m.width;
+	run_kernel(s, KD_NORM, (double)R * W * (4 + act_size(s)), 0, [&] {
+		if (s.m.exact) launch_k(s, k_seq_rms<float>, cdiv(R, 4), 128, 0, (float*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
+		else launch_k(s, k_seq_rms<bf16>, cdiv(R, 4), 128, 0, (bf16*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
+	});
+}
 void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R) {
 	const size_t n = (size_t)R * s.m.width;
 	run_kernel(s, KD_NORM, n * (4 + act_size(s)), 0, [&] {
@@ -307,22 +377,28 @@ void attention_products(Seq& s, int kind, const AttArgs& a, bf16* out, const Seq
 		const int q0 = pos0 + t0;
 		int Tb = count - t0;
 		while (Tb > 64 && (size_t)a.group * Tb * (size_t)(q0 + Tb) > budget) Tb = (Tb + 1) / 2;
-		const int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0, C = q0 + Tb - k0, Cp = (C + 7) & ~7;
+		// gathered keys: the kept first positions the block's window has left behind, then everything from the first query's window on
+		const int k0 = a.window > 0 ? std::max(0, q0 - a.window + 1) : 0, kfb = a.window > 0 ? std::min(a.keep_first, k0) : 0;
+		const int C = kfb + q0 + Tb - k0, Cp = (C + 7) & ~7;
 		reserve_attn(s, (size_t)C * a.kd, (size_t)a.vd * Cp, (size_t)a.group * Tb * Cp);
 		for (int kvh = 0; kvh < G; ++kvh) {
 			AttGather g;
 			g.kc = a.kc, g.vc = a.vc, g.kld = a.kld, g.vld = a.vld, g.kcol = kvh * a.kd, g.vcol = kvh * a.vd, g.kd = a.kd, g.vd = a.vd;
-			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp;
+			g.Kb = s.att_kb, g.Vt = s.att_vt, g.slot = slot, g.k0 = k0, g.C = C, g.Cp = Cp, g.kfb = kfb;
 			run_kernel(s, kind, (double)C * (a.kd + a.vd) * 6, 0, [&] { launch_k(s, k_seq_attn_gather, dim3(cdiv(Cp, 32), 4), 256, 0, g, sb); });
 			const int h0 = kvh * a.group;
 			const bf16* q = (const bf16*)s.a3 + ((size_t)(first + t0) * a.heads + h0) * a.kd;
 			gemm(s, q, (long)a.heads * a.kd, a.kd, s.att_kb, a.kd, 0, s.att_s, Cp, (long)Tb * Cp, Tb, C, a.kd, a.group, EPI_F32, nullptr, kind, false);
 			AttSoftmax sm;
 			sm.S = s.att_s, sm.P = s.att_p, sm.T = Tb, sm.C = C, sm.Cp = Cp, sm.qpos0 = q0, sm.k0 = k0, sm.window = a.window, sm.scale = a.scale;
-			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = a.gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
+			sm.keep_first = a.window > 0 ? a.keep_first : 0, sm.kfb = kfb;
+			const bool head_gate = a.gate && a.ges == 0; // one gate per head scales the probabilities; a gate per channel goes into the value product's epilogue
+			sm.sink = a.sink ? a.sink + h0 : nullptr, sm.gate = head_gate ? a.gate + (size_t)(first + t0) * a.ldg + h0 : nullptr, sm.ldg = a.ldg;
+			GemmExtra gx;
+			if (a.gate && !head_gate) gx.gate = a.gate + (size_t)(first + t0) * a.ldg + (size_t)h0 * a.ghs, gx.ldgate = a.ldg, gx.gbs = a.ghs;
 			run_kernel(s, kind, (double)a.group * Tb * Cp * 6, 0, [&] { launch_k(s, k_seq_attn_softmax, dim3(Tb, a.group), 256, 0, sm); });
 			gemm(s, s.att_p, Cp, (long)Tb * Cp, s.att_vt, Cp, 0, out + ((size_t)(first + t0) * a.heads + h0) * a.vd, (long)a.heads * a.vd, a.vd, Tb, a.vd, C, a.group,
-			     EPI_ACT, nullptr, kind, false);
+			     EPI_ACT, nullptr, kind, false, &gx);
 		}
 		t0 += Tb;
 	}
@@ -343,7 +419,7 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 	const size_t smem = attn_smem(a.tile, a.kd);
 	// few tokens over a long context: the keys of one (token, head tile) are shared out over several CTAs
 	const int live = a.skip ? std::max(1, sb.N - s.tok_on_products) : sb.N; // tokens the fused kernel really serves (the others' CTAs leave at once)
-	a.nsplit = attn_nsplit(s, live, a.heads / a.tile, a.window, longest);
+	a.nsplit = attn_nsplit(s, live, a.heads / a.tile, a.window > 0 ? a.window + a.keep_first : 0, longest);
 	ensure_part(s, (size_t)sb.N * a.heads * a.nsplit * (a.vd + 2));
 	a.part = s.part;
 	const dim3 grid(sb.N, a.heads / a.tile, a.nsplit);
@@ -369,11 +445,31 @@ void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& 
 		run_kernel(s, KD_CONV, 0, 0, [&] { launch_k(s, k_seq_conv_state, dim3(cdiv(ca.channels, 128), sb.B), 128, 0, r.conv, s.proj, ca.ldp, L.taps, ca.channels, sb); });
 }
 
+// how a sublayer's last product lands in the stream: serial blocks apply the Dynamic Tanh norm after the sublayer and add
+// (EPI_DYT_RES into x); parallel blocks park the mixer's output (EPI_F32 into `mo`) and add it together with the feed-forward's
+// (EPI_RES into x with res = mo), or add it alone when the layer has no feed-forward
+struct OutEpi {
+	int epi;
+	const SeqNorm* nrm;
+	float* dst;
+	const float* res;
+};
 template <typename AT>
-void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest) {
+void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi& oe) {
+	GemmExtra gx;
+	gx.res = oe.res;
+	gemm(s, X, K, 0, Wt, K, 0, oe.dst, s.m.width, 0, N, s.m.width, K, 1, oe.epi, oe.nrm, -1, true, &gx);
+}
+
+template <typename AT>
+void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const OutEpi& oe) {
 	const int N = sb.N, W = s.m.width, P = (int)in_rows(L);
 	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
-	gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, P, W, 1, EPI_F32);
+	{
+		GemmExtra gx;
+		gx.bias = L.b_in;
+		gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, P, W, 1, EPI_F32, nullptr, -1, true, &gx);
+	}
 	if (L.type == SEQ_LATENT) {
 		const int H = L.heads, D = L.dim, Dv = L.vdim, Rq = L.q_rank, Rk = L.kv_rank;
 		RmsSeg sq{0, Rq, (const bf16*)L.dq_norm}, sc{Rq, Rk, (const bf16*)L.dkv_norm};
@@ -384,10 +480,10 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		gemm(s, a2, (long)H * D, D, L.w_ukT, D, (long)Rk * D, s.f[0], (long)H * Rk, Rk, N, Rk, D, H, EPI_F32);
 		AttArgs a;
 		a.q = s.f[0], a.kc = a.vc = r.cache_a, a.kld = a.vld = Rk, a.heads = H, a.group = H, a.tile = attn_tile(H, Rk, Rk), a.kd = a.vd = Rk, a.window = 0;
-		a.scale = L.scale, a.sink = nullptr, a.gate = s.proj + Rq + Rk, a.ldg = P;
+		a.scale = L.scale, a.sink = nullptr, a.gate = s.proj + Rq + Rk, a.ldg = P, a.ghs = 1, a.ges = 0, a.keep_first = 0;
 		attention(s, KD_ATTN_LATENT, a, a1, sb, kv_rows, longest);
 		gemm(s, a1, (long)H * Rk, Rk, L.w_uv, Rk, (long)Dv * Rk, a2, (long)H * Dv, Dv, N, Dv, Rk, H, EPI_ACT);
-		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
 	} else if (L.type == SEQ_DELTA) {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		const int cq = 0, ck = G * D, cv = 2 * G * D, cb = cv + H * Dv, ca1 = cb + H, cg1 = ca1 + L.a_rank;
@@ -417,8 +513,48 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 			else launch_k(s, k_seq_delta_scan, dim3(sb.B, H), threads, smem, d, sb);
 		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0,
-		           [&] { launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.f[4], (const bf16*)L.out_norm, N, H, Dv, s.m.eps); });
-		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+		           [&] { launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.f[4], H * Dv, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 0); });
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+	} else if (L.type == SEQ_GQA) {
+		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
+		QkArgs qa;
+		qa.proj = s.proj, qa.ldp = P, qa.heads = H, qa.kv_heads = G, qa.dim = D, qa.vdim = Dv, qa.qw = (const bf16*)L.q_norm, qa.kw = (const bf16*)L.k_norm, qa.eps = s.m.eps;
+		qa.rot_dims = L.rot_dims, qa.freq = s.rot_freq[r.layer], qa.mag = s.rot_mag[r.layer], qa.q = s.f[0], qa.kc = r.cache_a, qa.vc = r.cache_b;
+		run_kernel(s, KD_QK, (double)N * (H * D + G * D + G * Dv) * 8, 0, [&] { launch_k(s, k_seq_qk_rope, N, 256, (size_t)std::max(L.rot_dims, 1) * sizeof(float), qa, sb); });
+		AttArgs a;
+		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
+		a.window = L.window, a.keep_first = L.window > 0 ? L.keep_first : 0, a.scale = L.scale, a.sink = nullptr;
+		a.gate = s.proj + H * D + G * D + G * Dv, a.ldg = P, a.ghs = Dv, a.ges = 1; // a sigmoid gate per output channel, from the same stacked projection
+		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * (L.window + L.keep_first)) : kv_rows, longest);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
+	} else if (L.type == SEQ_GLA) {
+		const int H = L.heads, D = L.dim, Dv = L.vdim;
+		const int cq = 0, ck = H * D, cv = 2 * H * D, cg = cv + H * Dv, ca1 = cg + H * Dv;
+		run_kernel(s, KD_ELEMENT, (double)N * L.a_rank * 6, 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv((long)N * L.a_rank, 256), 256, 0, a1, s.proj, P, ca1, L.a_rank, N); });
+		{
+			GemmExtra gx;
+			gx.bias = L.b_a2;
+			gemm(s, a1, L.a_rank, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_F32, nullptr, -1, true, &gx);
+		}
+		GlaArgs g;
+		g.proj = s.proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.z = s.f[3], g.zb = nullptr, g.inv_tau = 1.f / L.tau, g.qscale = 1.f / sqrtf((float)D);
+		g.state = r.delta, g.o = s.f[5], g.heads = H, g.dim = D, g.vdim = Dv;
+		const int rows = cdiv(D, 4);
+		const int R = rows <= 8 ? 8 : rows <= 16 ? 16 : rows <= 24 ? 24 : rows <= 32 ? 32 : 64;
+		const int threads = std::min(256, cdiv(4 * Dv, 32) * 32);
+		const dim3 grid(sb.B, H, cdiv(4 * Dv, threads));
+		const size_t smem = (size_t)3 * GLA_TB * R * 4 * sizeof(float);
+		run_kernel(s, KD_GLA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 4.0, [&] {
+			if (R == 8) launch_k(s, k_seq_gla_scan<8, 4>, grid, threads, smem, g, sb);
+			else if (R == 16) launch_k(s, k_seq_gla_scan<16, 4>, grid, threads, smem, g, sb);
+			else if (R == 24) launch_k(s, k_seq_gla_scan<24, 4>, grid, threads, smem, g, sb);
+			else if (R == 32) launch_k(s, k_seq_gla_scan<32, 4>, grid, threads, smem, g, sb);
+			else launch_k(s, k_seq_gla_scan<64, 4>, grid, threads, smem, g, sb);
+		});
+		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] {
+			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
+		});
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
 	} else {
 		const int H = L.heads, G = L.kv_heads, D = L.dim, Dv = L.vdim;
 		ConvArgs ca;
@@ -428,16 +564,63 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		conv(s, L, r, ca, sb);
 		AttArgs a;
 		a.q = s.f[0], a.kc = r.cache_a, a.vc = r.cache_b, a.kld = G * D, a.vld = G * Dv, a.heads = H, a.group = H / G, a.tile = attn_tile(H / G, D, Dv), a.kd = D, a.vd = Dv;
-		a.window = L.window, a.scale = L.scale, a.sink = (const bf16*)L.sink, a.gate = nullptr, a.ldg = 0;
+		a.window = L.window, a.scale = L.scale, a.sink = (const bf16*)L.sink, a.gate = nullptr, a.ldg = 0, a.ghs = 1, a.ges = 0, a.keep_first = 0;
 		attention(s, KD_ATTN_WINDOW, a, a2, sb, L.window > 0 ? std::min(kv_rows, (double)N * L.window) : kv_rows, longest);
-		gemm(s, a2, (long)H * Dv, 0, L.w_o, (long)H * Dv, 0, s.x, W, 0, N, W, H * Dv, 1, EPI_DYT_RES, &L.norm1b);
+		out_product<AT>(s, a2, L.w_o, N, H * Dv, oe);
 	}
-	if (L.ff > 0) {
-		dyt(s, s.hA, s.x, nullptr, L.norm2, N);
+}
+
+// the feed-forward of a layer on the normed rows in hA
+template <typename AT>
+void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& oe) {
+	const int N = sb.N, W = s.m.width;
+	AT *hA = (AT*)s.hA, *a2 = (AT*)s.a2;
+	if (L.ff_kind == SEQ_FF_CLAMPED) {
 		gemm(s, hA, W, 0, L.w_gate_up, W, 0, s.proj, 2L * L.ff, 0, N, 2 * L.ff, W, 1, EPI_F32);
 		run_kernel(s, KD_ELEMENT, (double)N * L.ff * (8 + sizeof(AT)), 0,
-		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit); });
-		gemm(s, a2, L.ff, 0, L.w_down, L.ff, 0, s.x, W, 0, N, W, L.ff, 1, EPI_DYT_RES, &L.norm2b);
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit, 0); });
+		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
+	} else if (L.ff_kind == SEQ_FF_RELU2) {
+		gemm(s, hA, W, 0, L.w_gate_up, W, 0, a2, L.ff, 0, N, L.ff, W, 1, EPI_ACT_RELU2); // relu(up)^2 leaves the product's epilogue in the activation type
+		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
+	} else {
+		// routed experts: logits -> choices and weights -> pairs grouped by expert -> two grouped products around the unit -> weighted sum
+		const int E = L.experts, top = L.top, pairs = N * top, ff = L.ff;
+		GemmExtra rx;
+		rx.bias = L.b_router;
+		gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, E, 0, N, E, W, 1, EPI_F32, nullptr, -1, true, &rx);
+		run_kernel(s, KD_ROUTE, (double)N * E * 4, 0, [&] { launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, s.proj, E, top, N, s.moe_sel, s.moe_wt); });
+		run_kernel(s, KD_ROUTE, (double)pairs * 4 * E, 0, [&] { launch_k(s, k_seq_moe_group, E, 256, 0, s.moe_sel, pairs, E, s.moe_seg, s.moe_perm, s.moe_inv); });
+		run_kernel(s, KD_ELEMENT, (double)pairs * W * 2 * sizeof(AT), 0,
+		           [&] { launch_k(s, k_seq_moe_gather<AT>, cdiv((long)pairs * W, 256), 256, 0, (AT*)s.moe_x, hA, s.moe_perm, top, pairs, W); });
+		GemmExtra gx;
+		gx.seg = s.moe_seg, gx.x_rows = pairs;
+		gemm(s, s.moe_x, W, 0, L.w_gate_up, W, 2L * ff * W, s.moe_y, 2L * ff, 0, N, 2 * ff, W, E, EPI_F32, nullptr, -1, true, &gx);
+		run_kernel(s, KD_ELEMENT, (double)pairs * ff * (8 + sizeof(AT)), 0,
+		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)pairs * ff, 256), 256, 0, (AT*)s.moe_a, s.moe_y, ff, pairs, 0.f, 1); });
+		gemm(s, s.moe_a, ff, 0, L.w_down, ff, (long)W * ff, s.moe_d, W, 0, N, W, ff, E, EPI_F32, nullptr, -1, true, &gx);
+		run_kernel(s, KD_ELEMENT, (double)N * W * (8 + 4.0 * top) + (oe.res ? (double)N * W * 4 : 0), 0, [&] {
+			launch_k(s, k_seq_moe_combine, cdiv((long)N * W, 256), 256, 0, oe.dst, oe.res, s.moe_d, s.moe_inv, s.moe_wt, top, N, W);
+		});
+	}
+}
+
+// one run of a layer: norm, mixer, feed-forward, in the model's block form
+template <typename AT>
+void layer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest) {
+	const int N = sb.N;
+	norm(s, s.hA, s.x, nullptr, L.norm1, N);
+	if (s.m.block == SEQ_BLOCK_SERIAL) {
+		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_DYT_RES, &L.norm1b, s.x, nullptr});
+		if (L.ff > 0) {
+			norm(s, s.hA, s.x, nullptr, L.norm2, N);
+			feed_forward<AT>(s, L, sb, OutEpi{EPI_DYT_RES, &L.norm2b, s.x, nullptr});
+		}
+	} else if (L.ff > 0) { // x += mixer(h) + ff(h): the mixer's output waits in `mo` for the feed-forward's last kernel
+		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_F32, nullptr, s.mo, nullptr});
+		feed_forward<AT>(s, L, sb, OutEpi{EPI_RES, nullptr, s.x, s.mo});
+	} else {
+		mixer_typed<AT>(s, L, r, sb, kv_rows, longest, OutEpi{EPI_RES, nullptr, s.x, nullptr});
 	}
 }
 
@@ -447,7 +630,7 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 	const int N = sb.N;
 	const bool looped = m.loop_times > 1;
 	run_kernel(s, KD_EMBED, (double)N * m.width * 6, 0,
-	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width); });
+	           [&] { launch_k(s, k_seq_embed, N, 128, 0, s.x, looped ? s.x0 : nullptr, (const bf16*)m.embed, s.d_tok, N, m.width, m.embed_scale != 0.f ? m.embed_scale : 1.f); });
 	for (size_t ri = 0; ri < s.runs.size(); ++ri) {
 		RunState& r = s.runs[ri];
 		const SeqLayer& L = s.layers[r.layer];
@@ -455,14 +638,13 @@ void forward(Seq& s, const SeqBatch& sb, int n_want, double kv_rows, int longest
 			const size_t n = (size_t)N * m.width;
 			run_kernel(s, KD_ELEMENT, n * 12.0, 0, [&] { launch_k(s, k_seq_add, cdiv(n, 256), 256, 0, s.x, s.x0, n); });
 		}
-		dyt(s, s.hA, s.x, nullptr, L.norm1, N);
-		if (m.exact) mixer_typed<float>(s, L, r, sb, kv_rows, longest);
-		else mixer_typed<bf16>(s, L, r, sb, kv_rows, longest);
+		if (m.exact) layer_typed<float>(s, L, r, sb, kv_rows, longest);
+		else layer_typed<bf16>(s, L, r, sb, kv_rows, longest);
 		if (s.trace)
 			CUDA_CHECK(cudaMemcpyAsync(s.trace_buf + ri * (size_t)N * m.width, s.x, (size_t)N * m.width * sizeof(float), cudaMemcpyDeviceToDevice, s.stream));
 	}
 	if (n_want) {
-		dyt(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
+		norm(s, s.hW, s.x, s.d_want, m.final_norm, n_want);
 		gemm(s, s.hW, m.width, 0, m.head, m.width, 0, s.logits, m.vocab, 0, n_want, m.vocab, m.width, 1, EPI_F32);
 	}
 }
@@ -474,10 +656,11 @@ void forward_decode_graph(Seq& s, const SeqBatch& sb, int n_want, double kv_rows
 	size_t part_need = 0;
 	for (const RunState& r : s.runs) {
 		const SeqLayer& L = s.layers[r.layer];
-		if (L.type == SEQ_DELTA) continue;
+		if (L.type == SEQ_DELTA || L.type == SEQ_GLA) continue;
 		const bool lat = L.type == SEQ_LATENT;
 		const int group = lat ? L.heads : L.heads / L.kv_heads, kd = lat ? L.kv_rank : L.dim, vd = lat ? L.kv_rank : L.vdim;
-		const int ns = attn_nsplit(s, sb.N, L.heads / attn_tile(group, kd, vd), lat ? 0 : L.window, longest);
+		const int span = lat || L.window <= 0 ? 0 : L.window + (L.type == SEQ_GQA ? L.keep_first : 0);
+		const int ns = attn_nsplit(s, sb.N, L.heads / attn_tile(group, kd, vd), span, longest);
 		key.push_back(ns);
 		part_need = std::max(part_need, (size_t)sb.N * L.heads * ns * (vd + 2));
 	}
@@ -561,11 +744,11 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 	for (RunState& r : s.runs) {
 		const SeqLayer& L = s.layers[r.layer];
 		if (L.type == SEQ_LATENT) r.cache_a = (float*)dalloc(rows * L.kv_rank * sizeof(float));
-		if (L.type == SEQ_WINDOW) {
+		if (L.type == SEQ_WINDOW || L.type == SEQ_GQA) {
 			r.cache_a = (float*)dalloc(rows * L.kv_heads * L.dim * sizeof(float));
 			r.cache_b = (float*)dalloc(rows * L.kv_heads * L.vdim * sizeof(float));
 		}
-		if (L.type != SEQ_LATENT) {
+		if (L.type == SEQ_DELTA || L.type == SEQ_WINDOW) {
 			r.conv_per_slot = (size_t)std::max(L.taps - 1, 0) * conv_channels(L);
 			r.conv = (float*)dalloc(r.conv_per_slot * m.max_seqs * sizeof(float));
 		}
@@ -575,11 +758,43 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 			const size_t smem = ((size_t)L.dim * L.vdim + 3 * L.dim) * sizeof(float);
 			if (smem > 48 * 1024) CUDA_CHECK(cudaFuncSetAttribute(k_seq_delta_scan, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
 		}
+		if (L.type == SEQ_GLA) {
+			r.delta_per_slot = (size_t)L.heads * L.dim * L.vdim;
+			r.delta = (float*)dalloc(r.delta_per_slot * m.max_seqs * sizeof(float));
+		}
 	}
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+	// rotation tables of the grouped-query attentions: angle step per rotated pair (in double), rescaled between two wavelengths
+	s.rot_freq.assign(m.n_layers, nullptr), s.rot_mag.assign(m.n_layers, 1.f);
+	for (int i = 0; i < m.n_layers; ++i) {
+		const SeqLayer& L = s.layers[i];
+		if (L.type != SEQ_GQA || L.rot_dims < 2) continue;
+		const int dims = L.rot_dims, half = dims / 2;
+		std::vector<double> f(half);
+		for (int j = 0; j < half; ++j) f[j] = pow((double)L.rot_base, -2.0 * j / dims);
+		if (L.rot_factor > 0.f) {
+			// the pair whose wavelength fits `t` times into the original context: pairs below `lo` keep their step, pairs above `hi`
+			// turn `factor` times slower, a linear ramp between
+			auto where = [&](double t) { return dims * log((double)L.rot_original / (2.0 * M_PI * t)) / (2.0 * log((double)L.rot_base)); };
+			const double lo = std::max(floor(where(L.rot_fast)), 0.0), hi = std::min(ceil(where(L.rot_slow)), (double)dims - 1.0);
+			for (int j = 0; j < half; ++j) {
+				const double ramp = std::min(1.0, std::max(0.0, (j - lo) / std::max(hi - lo, 0.001)));
+				f[j] = f[j] / L.rot_factor * ramp + f[j] * (1.0 - ramp);
+			}
+			s.rot_mag[i] = (float)(0.1 * log((double)L.rot_factor) + 1.0);
+		}
+		s.rot_freq[i] = (double*)dalloc(half * sizeof(double));
+		CUDA_CHECK(cudaMemcpy(s.rot_freq[i], f.data(), half * sizeof(double), cudaMemcpyHostToDevice));
+	}
 	// workspace widths
 	for (const SeqLayer& L : s.layers) {
+		if (L.ff > 0 && L.ff_kind == SEQ_FF_MOE) {
+			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
+			s.w_proj = std::max(s.w_proj, (size_t)L.experts);
+		}
+		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max(s.w_a, (size_t)L.heads * L.vdim);
+		if (L.type == SEQ_GLA) s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim}), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.a_rank});
 		s.w_proj = std::max({s.w_proj, in_rows(L), (size_t)2 * L.ff});
 		size_t wf = 0, wa = (size_t)L.ff;
 		if (L.type == SEQ_LATENT) wf = (size_t)L.heads * L.kv_rank, wa = std::max({wa, (size_t)L.heads * L.kv_rank, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim, (size_t)L.q_rank});
@@ -599,6 +814,8 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	cudaFree(s->table_dev), cudaFree(s->d_tok), cudaFree(s->d_want), cudaFree(s->d_argmax), cudaFree(s->logits), cudaFree(s->hW);
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);
+	for (double* p : s->rot_freq) cudaFree(p);
+	cudaFree(s->mo), cudaFree(s->moe_sel), cudaFree(s->moe_wt), cudaFree(s->moe_y), cudaFree(s->moe_d), cudaFree(s->moe_x), cudaFree(s->moe_a);
 	for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
 	for (cudaEvent_t e : s->timer) cudaEventDestroy(e);
 	cudaStreamDestroy(s->stream);

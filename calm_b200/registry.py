@@ -17,9 +17,10 @@ def register(architecture: str, loader: Callable) -> None:
 
 
 def _defaults() -> None:
-    from . import vimulorn
+    from . import bovinex, vimulorn
 
     register(vimulorn.ARCHITECTURE, vimulorn.load)
+    register(bovinex.ARCHITECTURE, bovinex.load)
 
 
 def architecture_of(path: str) -> str:

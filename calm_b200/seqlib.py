@@ -11,7 +11,10 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SEQ_LATENT, SEQ_DELTA, SEQ_WINDOW = 0, 1, 2
+SEQ_LATENT, SEQ_DELTA, SEQ_WINDOW, SEQ_GQA, SEQ_GLA = 0, 1, 2, 3, 4
+NORM_DYT, NORM_RMS = 0, 1
+BLOCK_SERIAL, BLOCK_PARALLEL = 0, 1
+FF_CLAMPED, FF_RELU2, FF_MOE = 0, 1, 2
 _fptr = C.POINTER(C.c_float)
 _iptr = C.POINTER(C.c_int)
 
@@ -24,13 +27,17 @@ class SeqLayer(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("type", "heads", "kv_heads", "dim", "vdim", "q_rank", "kv_rank", "taps", "window", "a_rank", "g_rank", "ff")] + \
                [("scale", C.c_float), ("limit", C.c_float)] + [(n, SeqNorm) for n in ("norm1", "norm1b", "norm2", "norm2b")] + \
                [(n, C.c_void_p) for n in ("w_in", "w_o", "dq_norm", "dkv_norm", "w_uq", "w_ukT", "w_uv", "conv", "w_a2", "w_g2", "a_log", "dt_bias",
-                                          "out_norm", "sink", "w_gate_up", "w_down")]
+                                          "out_norm", "sink", "w_gate_up", "w_down", "b_in", "q_norm", "k_norm", "b_a2")] + \
+               [(n, C.c_int) for n in ("keep_first", "rot_dims")] + \
+               [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_original", "rot_fast", "rot_slow", "tau")] + \
+               [(n, C.c_int) for n in ("ff_kind", "experts", "top")] + [(n, C.c_void_p) for n in ("w_router", "b_router")]
 
 
 class SeqModel(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("vocab", "width", "n_layers", "loop_start", "loop_stop", "loop_times")] + [("eps", C.c_float)] + \
                [(n, C.c_int) for n in ("exact", "max_tokens", "max_seqs", "page")] + \
-               [("embed", C.c_void_p), ("head", C.c_void_p), ("final_norm", SeqNorm), ("layers", C.POINTER(SeqLayer))]
+               [("embed", C.c_void_p), ("head", C.c_void_p), ("final_norm", SeqNorm), ("layers", C.POINTER(SeqLayer)),
+                ("norm_kind", C.c_int), ("norm_offset", C.c_float), ("block", C.c_int), ("embed_scale", C.c_float)]
 
 
 _lib = None
@@ -76,7 +83,7 @@ class SeqError(RuntimeError):
 
 class SeqDeviceModel:
     """A layer-list model on the GPU.  `layers` are dicts of SeqLayer fields whose tensor-valued entries name tensors in
-    `tensors` (host torch tensors, uploaded here); see models/vimulorn.py for the host that fills them from a checkpoint."""
+    `tensors` (host torch tensors, uploaded here); vimulorn.py and bovinex.py are the hosts that fill them from a checkpoint."""
 
     def __init__(self, head: Dict[str, object], layers: List[Dict[str, object]], tensors: Dict[str, "object"], exact: bool = False,
                  max_tokens: int = 4096, max_seqs: int = 64, page: int = 16):
@@ -92,8 +99,8 @@ class SeqDeviceModel:
                 self._uploaded[name] = self.lib.calm_b200_seq_upload(t.data_ptr(), t.numel() * t.element_size())
             return self._uploaded[name]
 
-        def norm(prefix: str) -> SeqNorm:
-            return SeqNorm(ptr(prefix), ptr(prefix + ".b"), ptr(prefix + ".alpha"))
+        def norm(prefix: str) -> SeqNorm:  # an RMS norm has only its weight
+            return SeqNorm(ptr(prefix), ptr(prefix + ".b") if prefix + ".b" in tensors else None, ptr(prefix + ".alpha") if prefix + ".alpha" in tensors else None)
 
         self._layers = (SeqLayer * len(layers))()
         for rec, d in zip(self._layers, layers):
@@ -109,6 +116,8 @@ class SeqDeviceModel:
         m.loop_start, m.loop_stop, m.loop_times = head.get("loop_start", 0), head.get("loop_stop", 0), head.get("loop_times", 1)
         m.eps, m.exact, m.max_tokens, m.max_seqs, m.page = head["eps"], int(exact), int(max_tokens), int(max_seqs), int(page)
         m.embed, m.head, m.final_norm = ptr(head["embed"]), ptr(head["head"]), norm(head["final_norm"])
+        m.norm_kind, m.norm_offset = int(head.get("norm_kind", NORM_DYT)), float(head.get("norm_offset", 0.0))
+        m.block, m.embed_scale = int(head.get("block", BLOCK_SERIAL)), float(head.get("embed_scale", 1.0))
         m.layers = C.cast(self._layers, C.POINTER(SeqLayer))
         self.desc = m
         self.vocab, self.width = m.vocab, m.width

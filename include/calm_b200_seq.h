@@ -16,7 +16,17 @@
  *               unit-norm q and k, a [dim x vdim] fp32 state per head carried from token to token.
  *   SEQ_WINDOW  grouped-query attention behind short causal convolutions, unweighted RMS norm on q and k, a sliding
  *               window of `window` positions and a learned per-head sink in the softmax denominator.
- * Norms are Dynamic Tanh (tanh(alpha x) w + b), before and after each sublayer.  Feed-forward: clamped gated unit.
+ *   SEQ_GQA     grouped-query attention with biased projections, one RMS norm over the whole query (and key) projection,
+ *               rotation of the first rot_dims channels of every head (pairs i, i + rot_dims/2; frequencies optionally
+ *               rescaled between two wavelengths), a sliding window that also keeps the first keep_first positions, and a
+ *               sigmoid gate on every output channel.
+ *   SEQ_GLA     gated linear attention: a [dim x vdim] fp32 state per head, S <- diag(a) S + k v^T, o = S^T q, with a decay
+ *               a = sigmoid(.)^(1/tau) per key channel from a low-rank projection; per-head RMS norm and a SiLU gate on the output.
+ * Norms (SeqModel.norm_kind): Dynamic Tanh (tanh(alpha x) w + b), or RMS (x / sqrt(mean x^2 + eps) * (w + norm_offset)).
+ * Blocks (SeqModel.block): serial -- norm, mixer, norm, residual add, then the same around the feed-forward; parallel -- one
+ * norm whose output both the mixer and the feed-forward read, x <- x + (mixer + feed-forward).
+ * Feed-forward (SeqLayer.ff_kind): clamped gated unit, down(relu(up)^2), or a routed mixture of SiLU-gated experts (the `top`
+ * largest router logits, softmax over those only).
  * A span of layers can be run several times in a row with the same weights (loop_*), each pass with its own state.
  */
 #ifndef CALM_B200_SEQ_H
@@ -29,9 +39,12 @@
 extern "C" {
 #endif
 
-enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2 };
+enum SeqMixer { SEQ_LATENT = 0, SEQ_DELTA = 1, SEQ_WINDOW = 2, SEQ_GQA = 3, SEQ_GLA = 4 };
+enum SeqNormKind { SEQ_NORM_DYT = 0, SEQ_NORM_RMS = 1 };
+enum SeqBlock { SEQ_BLOCK_SERIAL = 0, SEQ_BLOCK_PARALLEL = 1 };
+enum SeqFfKind { SEQ_FF_CLAMPED = 0, SEQ_FF_RELU2 = 1, SEQ_FF_MOE = 2 };
 
-/* a Dynamic Tanh norm: bf16 weight[n], bf16 bias[n], bf16 alpha[1] (device pointers) */
+/* a norm: bf16 weight[n]; Dynamic Tanh also bf16 bias[n], bf16 alpha[1] (device pointers; NULL for an RMS norm) */
 struct SeqNorm {
 	const void* w;
 	const void* b;
@@ -52,7 +65,8 @@ struct SeqLayer {
 	float scale;         /* score scale of the attentions */
 	float limit;         /* clamp of the feed-forward */
 	struct SeqNorm norm1, norm1b, norm2, norm2b;
-	/* SEQ_LATENT: rows [dq | dkv | g];  SEQ_DELTA: [q | k | v | b | a1 | g1];  SEQ_WINDOW: [q | k | v] */
+	/* SEQ_LATENT: rows [dq | dkv | g];  SEQ_DELTA: [q | k | v | b | a1 | g1];  SEQ_WINDOW: [q | k | v];
+	 * SEQ_GQA: [q | k | v | g];  SEQ_GLA: [q | k | v | g | a1] */
 	const void* w_in;
 	const void* w_o;       /* (width, heads*vdim) */
 	/* SEQ_LATENT */
@@ -72,8 +86,23 @@ struct SeqLayer {
 	/* SEQ_WINDOW */
 	const void* sink;      /* bf16 [heads] or NULL */
 	/* feed-forward */
-	const void* w_gate_up; /* rows [gate | up]: (2*ff, width) */
-	const void* w_down;    /* (width, ff) */
+	const void* w_gate_up; /* rows [gate | up]: (2*ff, width); SEQ_FF_RELU2: up only (ff, width); SEQ_FF_MOE: [experts](2*ff, width) */
+	const void* w_down;    /* (width, ff); SEQ_FF_MOE: [experts](width, ff) */
+	/* SEQ_GQA / SEQ_GLA */
+	const void* b_in;      /* bf16 bias of the stacked input projection (rows of w_in), or NULL */
+	const void* q_norm;    /* SEQ_GQA: bf16 [heads*dim], weight of the RMS norm over the whole query projection, or NULL */
+	const void* k_norm;    /* SEQ_GQA: bf16 [kv_heads*dim] */
+	const void* b_a2;      /* SEQ_GLA: bf16 [heads*dim], bias of the decay projection */
+	int keep_first;        /* SEQ_GQA: the first positions every query keeps seeing (with `window`) */
+	int rot_dims;          /* SEQ_GQA: rotated channels per head (even, <= dim; 0: none) */
+	float rot_base;
+	float rot_factor;      /* frequency rescaling between two wavelengths; <= 0: none */
+	float rot_original, rot_fast, rot_slow;
+	float tau;             /* SEQ_GLA: decay = sigmoid(.)^(1/tau) */
+	int ff_kind;           /* enum SeqFfKind; ff is the width of one expert for SEQ_FF_MOE */
+	int experts, top;      /* SEQ_FF_MOE */
+	const void* w_router;  /* (experts, width) */
+	const void* b_router;  /* bf16 [experts] or NULL */
 };
 
 struct SeqModel {
@@ -88,6 +117,10 @@ struct SeqModel {
 	const void* head;   /* bf16 (vocab, width) */
 	struct SeqNorm final_norm;
 	const struct SeqLayer* layers;
+	int norm_kind;      /* enum SeqNormKind */
+	float norm_offset;  /* SEQ_NORM_RMS: added to the stored weight (1 for weights stored around zero) */
+	int block;          /* enum SeqBlock */
+	float embed_scale;  /* factor on the embedding rows (0 is read as 1) */
 };
 
 /* cudaMalloc + copy, like upload_cuda */
