@@ -793,7 +793,7 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 			s.max_top = std::max(s.max_top, L.top), s.max_experts = std::max(s.max_experts, L.experts), s.w_moe_ff = std::max(s.w_moe_ff, (size_t)L.ff);
 			s.w_proj = std::max(s.w_proj, (size_t)L.experts);
 		}
-		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max(s.w_a, (size_t)L.heads * L.vdim);
+		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
 		if (L.type == SEQ_GLA) s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim}), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.a_rank});
 		s.w_proj = std::max({s.w_proj, in_rows(L), (size_t)2 * L.ff});
 		size_t wf = 0, wa = (size_t)L.ff;
