@@ -735,80 +735,145 @@ __global__ void k_seq_delta_out(AT* out, const float* o, const float* gate, int 
 }
 
 // ---------------------------------------------------------------- gated linear attention
-// Per (sequence, head): S [dim][vdim] fp32;  per token  S <- diag(a) S + k v^T,  o = S^T q  with one decay per key channel,
-// a = sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau), formed here in fp32 from the raw decay projection z (+ bias).
-// q, k, v are columns of the stacked projection (row stride ldp); q is scaled by qscale.
+// Per (sequence, head): S [dim][vdim] fp32;  per token  S <- diag(a) S + k v^T,  o = S^T q * qscale  with one decay a per key
+// channel (formed in fp32 by the decay projection's epilogue, EPI_DECAY).  q, k, v are columns of the stacked projection (row
+// stride ldp).
 struct GlaArgs {
 	const float* proj;
 	int ldp, qcol, kcol, vcol;
-	const float* z;      // [N][heads*dim] raw decay projection
-	const bf16* zb;      // [heads*dim] bias or null
-	float inv_tau, qscale;
-	float* state;        // [slots][heads][dim][vdim]
+	const float* decay;  // [N][heads*dim]
+	float qscale;
+	float* state;        // [slots][heads][vdim][ldstate]: a value column's key channels side by side (channels past dim stay zero)
+	int ldstate;
 	float* o;            // [N][heads*vdim]
 	int heads, dim, vdim;
+	int vec;             // rows, columns and bases are 16-byte aligned: tokens are staged with 16-byte copies instead of 4-byte ones
 };
-// The state sits in registers: GLA_P lanes share a value column, each holding dim / GLA_P of its rows (R per lane).  Tokens are staged
-// GLA_TB at a time into shared memory (k, scaled q, decay; v is read by the column's lanes directly), so the loop over a block's
-// tokens has no barrier inside, only the shuffles that fold a column's partial read-outs.
-#define GLA_TB 8
-template <int R, int GLA_P>
-__global__ void __launch_bounds__(256) k_seq_gla_scan(GlaArgs a, SeqBatch sb) {
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// One CTA of 128 threads per (sequence, head, 128 / P value columns).  The state sits in registers: P lanes share a value column,
+// each holding R of its key channels (P = 4, 8 or 16: the host takes more lanes per column when sequences x heads alone would
+// leave SMs idle, since per token a warp issues ~3 R arithmetic instructions and that, not memory, bounds a long prompt).
+// Tokens are staged GLA_TB at a time into a double buffer with asynchronous copies (k, q and the decay in P segments padded by 4
+// floats, so that the lanes of a column read different banks as float4; the CTA's values of v), so a block's tokens are applied
+// without a barrier between them -- log2(P) shuffles fold a column's read-out -- while the next block travels.  Read-outs
+// leave through shared memory, one coalesced store per block.
+#define GLA_TB 16
+template <int R, int P>
+__global__ void __launch_bounds__(128) k_seq_gla_scan(GlaArgs a, SeqBatch sb) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
+	constexpr int QP = R + 4, VC = 128 / P, TOK = 3 * P * QP + VC;
 	extern __shared__ __align__(16) float sm[];
-	const int b = blockIdx.x, h = blockIdx.y, D = a.dim, V = a.vdim;
-	const int tid = threadIdx.x, part = tid % GLA_P;
-	const int v0 = blockIdx.z * (blockDim.x / GLA_P);      // value columns of this CTA
-	const int colx = v0 + tid / GLA_P;
-	const bool live = colx < V;
-	const int col = live ? colx : V - 1;                   // lanes past the last column run along on a copy of it (whole warps shuffle)
-	const int DP = R * GLA_P;                              // rows covered (>= D; rows past D hold zeros)
-	float* ks = sm;                                        // [GLA_TB][DP], row i of lane `part` at part * R + i
-	float* qs = ks + GLA_TB * DP;
-	float* gs = qs + GLA_TB * DP;
+	float* const buf0 = sm;
+	float* const obuf = sm + 2 * GLA_TB * TOK; // [2][GLA_TB][VC]
+	const int b = blockIdx.x, h = blockIdx.y, D = a.dim, V = a.vdim, v0 = blockIdx.z * VC;
+	const int tid = threadIdx.x, part = tid % P, cl = tid / P;
+	const bool live = v0 + cl < V;
+	const int start = sb.sstart[b], cnt = sb.scount[b], nblk = (cnt + GLA_TB - 1) / GLA_TB;
+	// the padding (channels past dim, columns past vdim) is never copied over: zero what this step will use, once
+	for (int i = tid; i < min(cnt, 2 * GLA_TB) * TOK; i += 128) sm[i] = 0.f;
 	float S[R];
-	float* Sg = a.state + ((size_t)sb.sslot[b] * a.heads + h) * D * V;
+	float* Sg = a.state + (((size_t)sb.sslot[b] * a.heads + h) * V + min(v0 + cl, V - 1)) * a.ldstate + part * R;
 #pragma unroll
-	for (int i = 0; i < R; ++i) S[i] = part * R + i < D ? Sg[(size_t)(part * R + i) * V + col] : 0.f;
-	const int start = sb.sstart[b], cnt = sb.scount[b];
-	for (int t0 = 0; t0 < cnt; t0 += GLA_TB) {
-		const int nt = min(GLA_TB, cnt - t0);
-		__syncthreads();
-		for (int e = tid; e < nt * DP; e += blockDim.x) {
-			const int tt = e / DP, i = e % DP;
-			float kv = 0.f, qv = 0.f, gv = 1.f;
-			if (i < D) {
-				const float* pr = a.proj + (size_t)(start + t0 + tt) * a.ldp;
-				kv = pr[a.kcol + h * D + i], qv = pr[a.qcol + h * D + i] * a.qscale;
-				const float z = a.z[(size_t)(start + t0 + tt) * a.heads * D + h * D + i] + (a.zb ? ldf(a.zb + h * D + i) : 0.f);
-				gv = expf(-softplusf_(-z) * a.inv_tau);
-			}
-			ks[e] = kv, qs[e] = qv, gs[e] = gv;
-		}
-		__syncthreads();
-		float vv[GLA_TB];
+	for (int i = 0; i < R; i += 4) {
+		const float4 t = *(const float4*)(Sg + i);
+		S[i] = t.x, S[i + 1] = t.y, S[i + 2] = t.z, S[i + 3] = t.w;
+	}
+	// 16-byte staging: a thread copies the same (at most two) chunks of every token, so where they come from and go to is worked out once
+	const float* vsrc[2] = {nullptr, nullptr};
+	long vstride[2] = {0, 0};
+	int vdst[2] = {0, 0};
+	if (a.vec) {
+		const int dc = D / 4;
 #pragma unroll
-		for (int tt = 0; tt < GLA_TB; ++tt) vv[tt] = tt < nt ? a.proj[(size_t)(start + t0 + tt) * a.ldp + a.vcol + h * V + col] : 0.f;
-#pragma unroll
-		for (int tt = 0; tt < GLA_TB; ++tt) {
-			if (tt < nt) {
-				const float *kp = ks + tt * DP + part * R, *qp = qs + tt * DP + part * R, *gp = gs + tt * DP + part * R;
-				float o = 0.f;
-#pragma unroll
-				for (int i = 0; i < R; ++i) {
-					S[i] = fmaf(gp[i], S[i], kp[i] * vv[tt]);
-					o = fmaf(S[i], qp[i], o);
-				}
-#pragma unroll
-				for (int w = 1; w < GLA_P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-				if (part == 0 && live) a.o[((size_t)(start + t0 + tt) * a.heads + h) * V + col] = o;
+		for (int r = 0; r < 2; ++r) {
+			const int c = tid + r * 128;
+			if (c < 3 * dc) {
+				const int sgm = c / dc, i = 4 * (c % dc);
+				vsrc[r] = sgm == 2 ? a.decay + ((size_t)start * a.heads + h) * D + i : a.proj + (size_t)start * a.ldp + (sgm == 0 ? a.kcol : a.qcol) + h * D + i;
+				vstride[r] = sgm == 2 ? (long)a.heads * D : a.ldp;
+				vdst[r] = sgm * P * QP + (i / R) * QP + i % R;
+			} else if (c < 3 * dc + VC / 4 && v0 + 4 * (c - 3 * dc) < V) {
+				const int i = 4 * (c - 3 * dc);
+				vsrc[r] = a.proj + (size_t)start * a.ldp + a.vcol + h * V + v0 + i, vstride[r] = a.ldp, vdst[r] = 3 * P * QP + i;
 			}
 		}
 	}
+	__syncthreads();
+	auto issue = [&](int blk) {
+		float* dst = buf0 + (blk & 1) * GLA_TB * TOK;
+		const int t0 = blk * GLA_TB, nt = min(GLA_TB, cnt - t0);
+		if (a.vec) {
+#pragma unroll
+			for (int r = 0; r < 2; ++r)
+				if (vsrc[r])
+					for (int tt = 0; tt < nt; ++tt) cp_async16(dst + tt * TOK + vdst[r], vsrc[r] + (t0 + tt) * vstride[r]);
+		} else {
+			const int per = 3 * D + VC;
+			for (int e = tid; e < nt * per; e += 128) {
+				const int tt = e / per, c = e % per;
+				const float* row = a.proj + (size_t)(start + t0 + tt) * a.ldp;
+				if (c < 3 * D) {
+					const int sgm = c / D, i = c % D;
+					const float* src = sgm == 0 ? row + a.kcol + h * D + i : sgm == 1 ? row + a.qcol + h * D + i : a.decay + ((size_t)(start + t0 + tt) * a.heads + h) * D + i;
+					cp_async4(dst + tt * TOK + sgm * P * QP + (i / R) * QP + i % R, src);
+				} else {
+					const int i = c - 3 * D;
+					if (v0 + i < V) cp_async4(dst + tt * TOK + 3 * P * QP + i, row + a.vcol + h * V + v0 + i);
+				}
+			}
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	auto write_out = [&](int blk) { // the read-outs of a finished block: consecutive threads, consecutive columns
+		const int nt = min(GLA_TB, cnt - blk * GLA_TB);
+		const float* ob = obuf + (blk & 1) * GLA_TB * VC;
+		for (int e = tid; e < nt * VC; e += 128) {
+			const int tt = e / VC, c = e % VC;
+			if (v0 + c < V) a.o[((size_t)(start + blk * GLA_TB + tt) * a.heads + h) * V + v0 + c] = ob[e];
+		}
+	};
+	issue(0);
+	for (int blk = 0; blk < nblk; ++blk) {
+		if (blk + 1 < nblk) {
+			issue(blk + 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else {
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
+		}
+		__syncthreads();
+		if (blk > 0) write_out(blk - 1);
+		const float* __restrict__ cur = buf0 + (blk & 1) * GLA_TB * TOK;
+		float* __restrict__ ob = obuf + (blk & 1) * GLA_TB * VC;
+		const int nt = min(GLA_TB, cnt - blk * GLA_TB);
+#pragma unroll 2
+		for (int tt = 0; tt < nt; ++tt) {
+			const float* tk = cur + tt * TOK;
+			const float4 *kp = (const float4*)(tk + part * QP), *qp = (const float4*)(tk + P * QP + part * QP), *gp = (const float4*)(tk + 2 * P * QP + part * QP);
+			const float v = tk[3 * P * QP + cl];
+			float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+			for (int i = 0; i < R / 4; ++i) {
+				const float4 g4 = gp[i], k4 = kp[i], q4 = qp[i];
+				S[4 * i] = fmaf(g4.x, S[4 * i], k4.x * v), S[4 * i + 1] = fmaf(g4.y, S[4 * i + 1], k4.y * v);
+				S[4 * i + 2] = fmaf(g4.z, S[4 * i + 2], k4.z * v), S[4 * i + 3] = fmaf(g4.w, S[4 * i + 3], k4.w * v);
+				o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1), o0 = fmaf(S[4 * i + 2], q4.z, o0), o1 = fmaf(S[4 * i + 3], q4.w, o1);
+			}
+			float o = o0 + o1;
+#pragma unroll
+			for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+			if (part == 0) ob[tt * VC + cl] = o * a.qscale;
+		}
+		__syncthreads(); // this block's buffer may be refilled and its read-outs are complete
+	}
+	write_out(nblk - 1);
 	if (live) {
 #pragma unroll
-		for (int i = 0; i < R; ++i)
-			if (part * R + i < D) Sg[(size_t)(part * R + i) * V + col] = S[i];
+		for (int i = 0; i < R; i += 4) *(float4*)(Sg + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
 	}
 }
 
@@ -972,7 +1037,7 @@ __global__ void k_seq_moe_combine(float* x, const float* res, const float* y, co
 
 // ---------------------------------------------------------------- products  Y[n][m] = sum_k X[n][k] W[m][k]
 // blockIdx.z = batch (per-head products): X, W, Y advance by xbs, wbs, ybs elements.
-enum { EPI_F32 = 0, EPI_ACT = 1, EPI_DYT_RES = 2, EPI_RES = 3, EPI_ACT_RELU2 = 4 };
+enum { EPI_F32 = 0, EPI_ACT = 1, EPI_DYT_RES = 2, EPI_RES = 3, EPI_ACT_RELU2 = 4, EPI_DECAY = 5 };
 struct GemmArgs {
 	const void* X;
 	long ldx, xbs;
@@ -982,7 +1047,9 @@ struct GemmArgs {
 	long ldy, ybs;
 	int N, M, K;
 	int epi;                 // EPI_F32: Y fp32; EPI_ACT: Y of the activation type; EPI_DYT_RES: Y fp32 residual += tanh(alpha acc) w + b;
-	                         // EPI_RES: Y fp32 residual += (res ? res : 0) + acc; EPI_ACT_RELU2: Y of the activation type = relu(acc)^2
+	                         // EPI_RES: Y fp32 residual += (res ? res : 0) + acc; EPI_ACT_RELU2: Y of the activation type = relu(acc)^2;
+	                         // EPI_DECAY: Y fp32 = sigmoid(acc)^epi_f = exp(-softplus(-acc) * epi_f)
+	float epi_f;
 	const bf16 *nw, *nb, *na;
 	int w_immutable;         // W is a model weight: it may be read before the previous kernel has finished (products of gathered keys set 0)
 	const bf16* bias;        // [batch][M] or null: added to the accumulator first
@@ -1011,6 +1078,7 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmR
 		if (a.gate) acc *= sigmoidf_(a.gate[(size_t)z * a.gbs + (size_t)(gr.base + n) * a.ldgate + m]);
 		((AT*)a.Y)[o] = to_act<AT>(acc);
 	} else if (a.epi == EPI_RES) ((float*)a.Y)[o] += a.res ? a.res[o] + acc : acc;
+	else if (a.epi == EPI_DECAY) ((float*)a.Y)[o] = expf(-softplusf_(-acc) * a.epi_f);
 	else if (a.epi == EPI_ACT_RELU2) {
 		const float r = fmaxf(acc, 0.f);
 		((AT*)a.Y)[o] = to_act<AT>(r * r);

@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <map>
+#include <type_traits>
 #include <vector>
 
 #include "seqkernels.cuh"
@@ -154,6 +155,27 @@ int conv_channels(const SeqLayer& L) {
 	if (L.type == SEQ_WINDOW) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim;
 	return 0;
 }
+// gated linear attention: key channels per lane when `lanes` lanes share a value column, the scan's shared memory, the row length
+// of a value column in the state (the same whichever lane count a step runs with), and the kernel's instantiations
+int gla_rows(int dim, int lanes) {
+	const int rows = cdiv(dim, lanes);
+	for (int r : {4, 8, 16, 24, 32, 64})
+		if (rows <= r && (r != 24 || lanes == 4) && (r != 4 || lanes != 4)) return r; // the instantiations of gla_each
+	return 64;
+}
+size_t gla_smem(int R, int lanes) { return ((size_t)2 * GLA_TB * (3 * lanes * (R + 4) + 128 / lanes) + 2 * GLA_TB * (128 / lanes)) * sizeof(float); }
+int gla_ldstate(int dim) { return std::max({4 * gla_rows(dim, 4), 8 * gla_rows(dim, 8), 16 * gla_rows(dim, 16)}); }
+template <typename F>
+void gla_each(F&& f) {
+	auto one = [&](auto r, auto p) { f(r, p); };
+	one(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{}), one(std::integral_constant<int, 16>{}, std::integral_constant<int, 4>{});
+	one(std::integral_constant<int, 24>{}, std::integral_constant<int, 4>{}), one(std::integral_constant<int, 32>{}, std::integral_constant<int, 4>{});
+	one(std::integral_constant<int, 64>{}, std::integral_constant<int, 4>{});
+	one(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}), one(std::integral_constant<int, 8>{}, std::integral_constant<int, 8>{});
+	one(std::integral_constant<int, 16>{}, std::integral_constant<int, 8>{}), one(std::integral_constant<int, 32>{}, std::integral_constant<int, 8>{});
+	one(std::integral_constant<int, 4>{}, std::integral_constant<int, 16>{}), one(std::integral_constant<int, 8>{}, std::integral_constant<int, 16>{});
+	one(std::integral_constant<int, 16>{}, std::integral_constant<int, 16>{});
+}
 // query heads per CTA of the attention kernel: divides the group, keeps the accumulators in registers and the queries in shared memory
 int attn_tile(int group, int kd, int vd) {
 	if (vd > 2 * ATT_THREADS) return 1; // wide values: one head per CTA
@@ -280,13 +302,14 @@ struct GemmExtra {
 	long ldgate = 0, gbs = 0;
 	const int* seg = nullptr;    // grouped product: rows of batch z
 	int x_rows = 0;              // grouped product: rows of X / Y over all groups
+	float epi_f = 0.f;           // EPI_DECAY: exponent
 };
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
           const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true, const GemmExtra* ex = nullptr) {
 	GemmArgs a;
 	const GemmExtra none;
 	if (!ex) ex = &none;
-	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows;
+	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
@@ -532,24 +555,27 @@ void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, dou
 		const int cq = 0, ck = H * D, cv = 2 * H * D, cg = cv + H * Dv, ca1 = cg + H * Dv;
 		run_kernel(s, KD_ELEMENT, (double)N * L.a_rank * 6, 0, [&] { launch_k(s, k_seq_cast_cols<AT>, cdiv((long)N * L.a_rank, 256), 256, 0, a1, s.proj, P, ca1, L.a_rank, N); });
 		{
-			GemmExtra gx;
-			gx.bias = L.b_a2;
-			gemm(s, a1, L.a_rank, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_F32, nullptr, -1, true, &gx);
+			GemmExtra gx; // the decay sigmoid(.)^(1/tau) leaves the product's epilogue in fp32
+			gx.bias = L.b_a2, gx.epi_f = 1.f / L.tau;
+			gemm(s, a1, L.a_rank, 0, L.w_a2, L.a_rank, 0, s.f[3], (long)H * D, 0, N, H * D, L.a_rank, 1, EPI_DECAY, nullptr, -1, true, &gx);
 		}
 		GlaArgs g;
-		g.proj = s.proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.z = s.f[3], g.zb = nullptr, g.inv_tau = 1.f / L.tau, g.qscale = 1.f / sqrtf((float)D);
+		g.proj = s.proj, g.ldp = P, g.qcol = cq, g.kcol = ck, g.vcol = cv, g.decay = s.f[3], g.qscale = 1.f / sqrtf((float)D);
 		g.state = r.delta, g.o = s.f[5], g.heads = H, g.dim = D, g.vdim = Dv;
-		const int rows = cdiv(D, 4);
-		const int R = rows <= 8 ? 8 : rows <= 16 ? 16 : rows <= 24 ? 24 : rows <= 32 ? 32 : 64;
-		const int threads = std::min(256, cdiv(4 * Dv, 32) * 32);
-		const dim3 grid(sb.B, H, cdiv(4 * Dv, threads));
-		const size_t smem = (size_t)3 * GLA_TB * R * 4 * sizeof(float);
+		g.vec = D % 4 == 0 && Dv % 4 == 0 && P % 4 == 0; // column offsets are then multiples of 4 as well, and cudaMalloc aligns the bases
+		g.ldstate = gla_ldstate(D);
+		// lanes per value column: more of them while sequences x heads x columns alone would leave SMs without a CTA
+		int lanes = 4;
+		while (lanes < 16 && (long)sb.B * H * cdiv(Dv * lanes, 128) < s.sms) lanes *= 2;
+		const int R = gla_rows(D, lanes);
+		const dim3 grid(sb.B, H, cdiv(Dv * lanes, 128));
+		const size_t smem = gla_smem(R, lanes);
 		run_kernel(s, KD_GLA, (double)N * H * (3.0 * D + 2.0 * Dv) * 4 + 2.0 * sb.B * H * D * Dv * 4, (double)N * H * D * Dv * 4.0, [&] {
-			if (R == 8) launch_k(s, k_seq_gla_scan<8, 4>, grid, threads, smem, g, sb);
-			else if (R == 16) launch_k(s, k_seq_gla_scan<16, 4>, grid, threads, smem, g, sb);
-			else if (R == 24) launch_k(s, k_seq_gla_scan<24, 4>, grid, threads, smem, g, sb);
-			else if (R == 32) launch_k(s, k_seq_gla_scan<32, 4>, grid, threads, smem, g, sb);
-			else launch_k(s, k_seq_gla_scan<64, 4>, grid, threads, smem, g, sb);
+			bool done = false;
+			gla_each([&](auto r, auto p) {
+				if (decltype(r)::value == R && decltype(p)::value == lanes) launch_k(s, k_seq_gla_scan<decltype(r)::value, decltype(p)::value>, grid, 128, smem, g, sb), done = true;
+			});
+			if (!done) CALM_FATAL("seq: no gated-linear-attention scan for %d key channels on %d lanes", D, lanes);
 		});
 		run_kernel(s, KD_NORM, (double)N * H * Dv * 10, 0, [&] {
 			launch_k(s, k_seq_delta_out<AT>, cdiv((long)N * H, 4), 128, 0, a2, s.f[5], s.proj + cg, P, (const bf16*)L.out_norm, N, H, Dv, s.m.eps, 1);
@@ -758,11 +784,15 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 			const size_t smem = ((size_t)L.dim * L.vdim + 3 * L.dim) * sizeof(float);
 			if (smem > 48 * 1024) CUDA_CHECK(cudaFuncSetAttribute(k_seq_delta_scan, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
 		}
-		if (L.type == SEQ_GLA) {
-			r.delta_per_slot = (size_t)L.heads * L.dim * L.vdim;
+		if (L.type == SEQ_GLA) { // the scan's own layout: a value column's key channels side by side, padded to its four lanes' share
+			r.delta_per_slot = (size_t)L.heads * L.vdim * gla_ldstate(L.dim);
 			r.delta = (float*)dalloc(r.delta_per_slot * m.max_seqs * sizeof(float));
 		}
 	}
+	gla_each([&](auto r, auto p) {
+		constexpr int R = decltype(r)::value, P = decltype(p)::value;
+		CUDA_CHECK(cudaFuncSetAttribute(k_seq_gla_scan<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gla_smem(R, P)));
+	});
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
 	CUDA_CHECK(cudaFuncSetAttribute(k_seq_attention<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
 	// rotation tables of the grouped-query attentions: angle step per rotated pair (in double), rescaled between two wavelengths

@@ -1,5 +1,7 @@
-"""Throughput of the Vimulorn family at layer sizes of real models (random weights), beside the calm engine's closest
-model -- a Llama-shaped stack of the same width, depth, head geometry and feed-forward width in fp16 -- on the same GPU.
+"""Throughput of the layer-list families at layer sizes of real models (random weights), each beside its closest existing
+model on the same GPU: Vimulorn beside a Llama-shaped stack of the same width, depth, head geometry and feed-forward width in
+fp16 on the calm engine; Bovinex beside Vimulorn at the same width, depth, head geometry, window and feed-forward width on
+the same runtime (both have windowed grouped-query attention and a recurrent mixer with a [dim x vdim] state per head).
 
 Per size: prompt throughput (one prompt of `prompt` tokens as one step), decode throughput for one sequence and for a
 batch, each after warm-up, timed with CUDA events on the library's stream; then one profiled pass that brackets every
@@ -9,6 +11,7 @@ are hundreds of MB), so no flush between iterations."""
 from __future__ import annotations
 
 import json
+import math
 import os
 import time
 from dataclasses import replace
@@ -36,6 +39,23 @@ def vimulorn_config(z: dict) -> dict:
     return {"architecture": "Vimulorn", "layers": block * z["blocks"], "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
 
 
+def bovinex_config(z: dict) -> dict:
+    """Blocks of [attention + dense, linear attention + routed experts, linear attention + dense]; two of eight experts of half the
+    dense width are active per token, which is the dense feed-forward's work in three matrices instead of two."""
+    H, D = z["heads"], z["dim"]
+    dense = {"ff": z["ff"], "kind": "dense"}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 2}, "router": {"experts": 8, "top": 2}}
+    rot = {"dims": D // 2, "base": 1e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    block = [
+        {"type": "attention", "mixer": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": D, "scale": D ** -0.5, "rot": rot,
+                                        "mask": {"size": z["window"], "keep_first": 64}}, "mlp": dense},
+        {"type": "gla", "mixer": {"heads": H, "dim": D, "vdim": D, "tau": 16.0, "a_rank": 64}, "mlp": moe},
+        {"type": "gla", "mixer": {"heads": H, "dim": D, "vdim": D, "tau": 16.0, "a_rank": 64}, "mlp": dense},
+    ]
+    return {"architecture": "Bovinex", "embedding": {"scale": math.sqrt(z["width"])}, "layers": block * z["blocks"], "norm": {"eps": 1e-5}, "vocab": z["vocab"],
+            "width": z["width"]}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -55,18 +75,18 @@ def roofline_table(stats: dict, hbm_gbs: float, tflops: float) -> dict:
     return out
 
 
-def bench_vimulorn(name: str, prompt: int, batch: int, steps: int, warmup: int, seed: int = 0) -> list:
-    from . import vimulorn
+def bench_family(family: str, name: str, prompt: int, batch: int, steps: int, warmup: int, seed: int = 0) -> list:
+    from . import bovinex, vimulorn
 
     z = SIZES[name]
-    cfg = vimulorn_config(z)
+    mod, cfg = (bovinex, bovinex_config(z)) if family == "bovinex" else (vimulorn, vimulorn_config(z))
     hbm, tf, src = peaks()
     t0 = time.time()
-    tensors = vimulorn.random_tensors(cfg, seed)
+    tensors = mod.random_tensors(cfg, seed)
     params = sum(t.numel() for t in tensors.values())
     rng = np.random.default_rng(seed)
     lines = []
-    with vimulorn.from_tensors(cfg, tensors, "bfloat16", max_tokens=(batch + 1) * (prompt + steps + warmup + 8), max_seqs=batch + 1, page=16) as m:
+    with mod.from_tensors(cfg, tensors, "bfloat16", max_tokens=(batch + 1) * (prompt + steps + warmup + 8), max_seqs=batch + 1, page=16) as m:
         del tensors
         toks = [int(x) for x in rng.integers(0, z["vocab"], prompt)]
 
@@ -85,7 +105,7 @@ def bench_vimulorn(name: str, prompt: int, batch: int, steps: int, warmup: int, 
         prefill_once()
         table = roofline_table(m.perf_stats(), hbm, tf)
         m.perf(False)
-        lines.append({"family": "vimulorn", "size": name, "phase": "prefill", "tokens": prompt, "ms": round(ms, 3), "tokens_per_s": round(prompt / ms * 1e3, 1),
+        lines.append({"family": family, "size": name, "phase": "prefill", "tokens": prompt, "ms": round(ms, 3), "tokens_per_s": round(prompt / ms * 1e3, 1),
                       "params": params, "kernels": table, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}})
         for b in sorted({1, batch}):
             slots = [m.open() for _ in range(b)]
@@ -103,7 +123,7 @@ def bench_vimulorn(name: str, prompt: int, batch: int, steps: int, warmup: int, 
             m.perf(False)
             for s in slots:
                 m.close_seq(s)
-            lines.append({"family": "vimulorn", "size": name, "phase": "decode", "batch": b, "context": prompt, "ms_per_step": round(ms, 4),
+            lines.append({"family": family, "size": name, "phase": "decode", "batch": b, "context": prompt, "ms_per_step": round(ms, 4),
                           "tokens_per_s": round(b / ms * 1e3, 1), "kernels": table})
     for ln in lines:
         ln["setup_s"] = round(time.time() - t0, 1)
@@ -141,16 +161,22 @@ def bench_llama_twin(name: str, prompt: int, steps: int, warmup: int, seed: int 
     return lines
 
 
-def main(sizes, prompt=2048, batch=16, steps=32, warmup=8, twin=True):
+def main(sizes, prompt=2048, batch=16, steps=32, warmup=8, twin=True, family="vimulorn"):
     from . import build as cbuild
 
     cbuild.build(target="seq")
-    if twin:
+    llama = twin and family == "vimulorn"
+    if llama:
         cbuild.build(target="engine")
     os.environ.setdefault("CALM_B200_QUIET", "1")
     out = []
     for name in sizes:
-        for ln in bench_vimulorn(name, prompt, batch, steps, warmup) + (bench_llama_twin(name, prompt, steps, warmup) if twin else []):
+        lines = bench_family(family, name, prompt, batch, steps, warmup)
+        if twin and family == "bovinex":
+            lines += bench_family("vimulorn", name, prompt, batch, steps, warmup)
+        if llama:
+            lines += bench_llama_twin(name, prompt, steps, warmup)
+        for ln in lines:
             print(json.dumps(ln), flush=True)
             out.append(ln)
     return out
