@@ -163,10 +163,10 @@ static inline const CUtensorMap* tg_map(const void* base, long rows, long cols, 
 	return &(g_tg.maps[key] = m);
 }
 
-// shapes the kernel takes: enough tokens to fill its tiles, 16-byte aligned rows and bases
+// shapes the kernel takes: enough tokens to fill its tiles (a matrix of few rows, a router's, fills the rest of its tile with the copy's zeros), 16-byte aligned rows and bases
 static inline bool gemm_tc_fits(const GemmArgs& a, int batch) {
 	auto al8 = [](long v) { return v % 8 == 0; };
-	return a.N >= 64 && a.M >= 32 && a.K >= 32 && al8(a.ldx) && al8(a.ldw) && al8(a.xbs) && al8(a.wbs) && ((uintptr_t)a.X & 15) == 0 && ((uintptr_t)a.W & 15) == 0 &&
+	return a.N >= 64 && a.M >= 8 && a.K >= 32 && al8(a.ldx) && al8(a.ldw) && al8(a.xbs) && al8(a.wbs) && ((uintptr_t)a.X & 15) == 0 && ((uintptr_t)a.W & 15) == 0 &&
 	       batch < 65536;
 }
 // false: no tensor map for one of the operands, nothing was launched

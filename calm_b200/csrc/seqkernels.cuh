@@ -79,34 +79,38 @@ __global__ void k_seq_dyt(AT* out, const float* x, const int* rows, const bf16* 
 	out[i] = to_act<AT>(tanhf(a * x[src]) * ldf(w + c) + ldf(b + c));
 }
 
-// RMS norm of whole rows: out[r][i] = x[row][i] / sqrt(mean(x[row]^2) + eps) * (w[i] + offset); one warp per row, the row is
-// read once (up to 32 * RMS_KEEP columns stay in registers, wider rows are read a second time)
-#define RMS_KEEP 32
+// RMS norm of whole rows: out[r][i] = x[row][i] / sqrt(mean(x[row]^2) + eps) * (w[i] + offset); one CTA per row (a single decoded
+// token of a wide model is one row: a warp alone would walk it in a hundred dependent steps), the row is read once (up to
+// blockDim * RMS_KEEP columns stay in registers, wider rows are read a second time)
+#define RMS_KEEP 16
 template <typename AT>
-__global__ void k_seq_rms(AT* out, const float* x, const int* rows, const bf16* w, float offset, float eps, int R, int width) {
+__global__ void __launch_bounds__(256) k_seq_rms(AT* out, const float* x, const int* rows, const bf16* w, float offset, float eps, int R, int width) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
-	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	const int r = blockIdx.x * (blockDim.x >> 5) + warp;
-	if (r >= R) return;
+	__shared__ float red[8];
+	const int tid = threadIdx.x, nt = blockDim.x, r = blockIdx.x;
 	const float* src = x + (size_t)(rows ? rows[r] : r) * width;
 	float keep[RMS_KEEP];
 	float ss = 0.f;
 #pragma unroll
 	for (int i = 0; i < RMS_KEEP; ++i) {
-		const int c = i * 32 + lane;
+		const int c = i * nt + tid;
 		keep[i] = c < width ? src[c] : 0.f;
 		ss = fmaf(keep[i], keep[i], ss);
 	}
-	for (int c = RMS_KEEP * 32 + lane; c < width; c += 32) ss = fmaf(src[c], src[c], ss);
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) ss = fmaf(src[c], src[c], ss);
 	ss = warp_sum(ss);
+	if ((tid & 31) == 0) red[tid >> 5] = ss;
+	__syncthreads();
+	ss = 0.f;
+	for (int i = 0; i < (nt >> 5); ++i) ss += red[i]; // every thread adds the warps' sums in the same order
 	const float rinv = 1.f / sqrtf(ss / (float)width + eps);
 	AT* d = out + (size_t)r * width;
 #pragma unroll
 	for (int i = 0; i < RMS_KEEP; ++i) {
-		const int c = i * 32 + lane;
+		const int c = i * nt + tid;
 		if (c < width) d[c] = to_act<AT>(keep[i] * rinv * (ldf(w + c) + offset));
 	}
-	for (int c = RMS_KEEP * 32 + lane; c < width; c += 32) d[c] = to_act<AT>(src[c] * rinv * (ldf(w + c) + offset));
+	for (int c = RMS_KEEP * nt + tid; c < width; c += nt) d[c] = to_act<AT>(src[c] * rinv * (ldf(w + c) + offset));
 }
 
 // RMS norm with a weight over `len` columns of src rows: segment s of blockIdx.y.  Segment 0 goes to an activation

@@ -353,8 +353,9 @@ void norm(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm,
 	if (s.m.norm_kind == SEQ_NORM_DYT) return dyt(s, out, x, rows, nm, R);
 	const int W = s.m.width;
 	run_kernel(s, KD_NORM, (double)R * W * (4 + act_size(s)), 0, [&] {
-		if (s.m.exact) launch_k(s, k_seq_rms<float>, cdiv(R, 4), 128, 0, (float*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
-		else launch_k(s, k_seq_rms<bf16>, cdiv(R, 4), 128, 0, (bf16*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
+		const int threads = std::min(256, std::max(32, cdiv(W, 4 * 32) * 32)); // about four columns per thread, whole warps
+		if (s.m.exact) launch_k(s, k_seq_rms<float>, R, threads, 0, (float*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
+		else launch_k(s, k_seq_rms<bf16>, R, threads, 0, (bf16*)out, x, rows, (const bf16*)nm.w, s.m.norm_offset, s.m.eps, R, W);
 	});
 }
 void dyt(Seq& s, void* out, const float* x, const int* rows, const SeqNorm& nm, int R) {
