@@ -854,8 +854,10 @@ __global__ void __launch_bounds__(128) k_seq_gla_scan(GlaArgs a, SeqBatch sb) {
 		const float* __restrict__ cur = buf0 + (blk & 1) * GLA_TB * TOK;
 		float* __restrict__ ob = obuf + (blk & 1) * GLA_TB * VC;
 		const int nt = min(GLA_TB, cnt - blk * GLA_TB);
-#pragma unroll 2
-		for (int tt = 0; tt < nt; ++tt) {
+		// the block's tokens, unrolled: each lane's share of a read-out stays in a register until the block is done, then the shares are
+		// folded for all tokens at once -- independent shuffles that overlap, instead of one dependent chain per token
+		float oacc[GLA_TB];
+		auto apply = [&](int tt) { // one token: decay, write, this lane's share of the read-out
 			const float* tk = cur + tt * TOK;
 			const float4 *kp = (const float4*)(tk + part * QP), *qp = (const float4*)(tk + P * QP + part * QP), *gp = (const float4*)(tk + 2 * P * QP + part * QP);
 			const float v = tk[3 * P * QP + cl];
@@ -867,11 +869,22 @@ __global__ void __launch_bounds__(128) k_seq_gla_scan(GlaArgs a, SeqBatch sb) {
 				S[4 * i + 2] = fmaf(g4.z, S[4 * i + 2], k4.z * v), S[4 * i + 3] = fmaf(g4.w, S[4 * i + 3], k4.w * v);
 				o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1), o0 = fmaf(S[4 * i + 2], q4.z, o0), o1 = fmaf(S[4 * i + 3], q4.w, o1);
 			}
-			float o = o0 + o1;
+			return o0 + o1;
+		};
+		if (nt == GLA_TB) { // a full block has no branch between its tokens: the loads of later tokens move up past the arithmetic of earlier ones
 #pragma unroll
-			for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-			if (part == 0) ob[tt * VC + cl] = o * a.qscale;
+			for (int tt = 0; tt < GLA_TB; ++tt) oacc[tt] = apply(tt);
+		} else {
+#pragma unroll
+			for (int tt = 0; tt < GLA_TB; ++tt) oacc[tt] = tt < nt ? apply(tt) : 0.f;
 		}
+#pragma unroll
+		for (int w = 1; w < P; w <<= 1)
+#pragma unroll
+			for (int tt = 0; tt < GLA_TB; ++tt) oacc[tt] += __shfl_xor_sync(0xffffffffu, oacc[tt], w);
+#pragma unroll
+		for (int tt = 0; tt < GLA_TB; ++tt)
+			if (tt % P == part) ob[tt * VC + cl] = oacc[tt] * a.qscale; // every lane of a column holds the sums: the lanes share the stores out
 		__syncthreads(); // this block's buffer may be refilled and its read-outs are complete
 	}
 	write_out(nblk - 1);
