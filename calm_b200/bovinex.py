@@ -1,5 +1,5 @@
-"""Bovinex: a decoder whose config.json lists its layers.  Every layer is a parallel block -- one RMS norm (weight stored
-around zero, applied as 1 + w) whose output feeds both a token mixer and a feed-forward, x <- x + (mixer + feed-forward).
+"""Bovinex: a decoder whose config.json lists its layers.  Every layer is a parallel block -- one RMS norm (the checkpoint keeps
+its weight as the offset from one: applied as 1 + w) whose output feeds both a token mixer and a feed-forward, x <- x + (mixer + feed-forward).
 Mixers: grouped-query attention (biased projections, one RMS norm over the whole query / key projection, partial rotation
 with frequencies rescaled between two wavelengths, a sliding window that keeps the first tokens, a sigmoid gate per output
 channel) and gated linear attention (a decaying [dim x vdim] state per head).  Feed-forward: down(relu(up)^2), or a routed
@@ -73,18 +73,27 @@ def plan(cfg: dict, tensors: Dict[str, torch.Tensor]) -> Tuple[dict, List[dict],
         rec["w_o"] = need(m + "o", [width, H * Dv])
         ml = lc.get("mlp")
         if ml:
+            # the block is parallel: what the feed-forward multiplies the normed input with first -- a dense unit's up rows, a
+            # router's rows -- rides at the end of the mixer's stacked input matrix (in_tail rows), one product for all of it
             f = p + "mlp."
+            n_in = up[rec["w_in"]].shape[0]
+            bias = up.pop(rec["b_in"]) if rec.get("b_in") else torch.zeros(n_in, dtype=torch.bfloat16)
             if ml["kind"] == "dense":
                 ff = int(ml["ff"])
-                rec.update(ff=ff, ff_kind=seqlib.FF_RELU2, w_gate_up=need(f + "up", [ff, width]), w_down=need(f + "down", [width, ff]))
+                tail, tail_b = up.pop(need(f + "up", [ff, width])), torch.zeros(ff, dtype=torch.bfloat16)
+                rec.update(ff=ff, ff_kind=seqlib.FF_RELU2, in_tail=ff, w_down=need(f + "down", [width, ff]))
             elif ml["kind"] == "moe":
                 ff, E, top = int(ml["expert"]["ff"]), int(ml["router"]["experts"]), int(ml["router"]["top"])
-                rec.update(ff=ff, ff_kind=seqlib.FF_MOE, experts=E, top=top, w_router=need(f + "router", [E, width]), b_router=need(f + "router.b", [E]))
+                tail, tail_b = up.pop(need(f + "router", [E, width])), up.pop(need(f + "router.b", [E]))
+                rec.update(ff=ff, ff_kind=seqlib.FF_MOE, experts=E, top=top, in_tail=E)
                 # experts side by side: [experts][gate | up] and [experts][down], so that one grouped product serves all of them
                 rec["w_gate_up"] = stack(f + "gate_up", [x for e in range(E) for x in (need(f + f"e{e}.gate", [ff, width]), need(f + f"e{e}.up", [ff, width]))])
                 rec["w_down"] = stack(f + "downs", [need(f + f"e{e}.down", [width, ff]) for e in range(E)])
             else:
                 raise ValueError(f"layer {i}: feed-forward kind {ml['kind']} is not part of this design")
+            up[rec["w_in"]] = torch.cat([up[rec["w_in"]], tail], 0).contiguous()
+            up[m + "in.b"] = torch.cat([bias, tail_b], 0)
+            rec["b_in"] = m + "in.b"
         layers.append(rec)
     head = {"vocab": vocab, "width": width, "eps": float(cfg["norm"]["eps"]), "embed": need("embed", [vocab, width]), "head": need("head", [vocab, width]),
             "final_norm": need("final.norm", [width]), "norm_kind": seqlib.NORM_RMS, "norm_offset": 1.0, "block": seqlib.BLOCK_PARALLEL,
@@ -149,7 +158,7 @@ def random_tensors(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
         leaf = name.split(".")[-1]
         if name.endswith("q.norm") or name.endswith("k.norm") or name.endswith("mix.norm"):
             t = 1.0 + 0.2 * torch.randn(shape, generator=g)
-        elif leaf in ("norm1", "norm"):  # the layer norms and final.norm: stored around zero
+        elif leaf in ("norm1", "norm"):  # the layer norms and final.norm: offsets from one
             t = 0.2 * torch.randn(shape, generator=g)
         elif name.endswith("a2.b"):
             t = 1.5 + 1.5 * torch.randn(shape, generator=g)

@@ -962,13 +962,13 @@ __global__ void __launch_bounds__(256) k_seq_qk_rope(QkArgs a, SeqBatch sb) {
 }
 
 // ---------------------------------------------------------------- routed experts
-// Router: per token the `top` largest logits (lowest index wins a tie), softmax over those only.  One warp per token.
-__global__ void k_seq_moe_route(const float* logits, int experts, int top, int N, int* sel, float* wt) {
+// Router: per token the `top` highest-scoring experts (lowest index wins a tie) and a softmax restricted to their scores.  One warp per token.
+__global__ void k_seq_moe_route(const float* logits, int ld, int experts, int top, int N, int* sel, float* wt) {
 	pdl_enter(); // programmatic dependent launch: let the next kernel's launch overlap this one, then wait for the previous one
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int n = blockIdx.x * (blockDim.x >> 5) + warp;
 	if (n >= N) return;
-	const float* z = logits + (size_t)n * experts;
+	const float* z = logits + (size_t)n * ld;
 	float first = 0.f, sum = 0.f;
 	for (int k = 0; k < top; ++k) {
 		float bv = -INFINITY;
@@ -1015,7 +1015,7 @@ __global__ void __launch_bounds__(256) k_seq_moe_group(const int* sel, int pairs
 		const int i = i0 + tid;
 		const bool mine = i < pairs && sel[i] == e;
 		const unsigned bal = __ballot_sync(0xffffffffu, mine);
-		__syncthreads(); // the previous round's readers of wsum / run_s are done
+		__syncthreads(); // the previous pass's readers of wsum / run_s are done
 		if (lane == 0) wsum[warp] = __popc(bal);
 		__syncthreads();
 		int before = run_s;
@@ -1075,6 +1075,9 @@ struct GemmArgs {
 	long ldgate, gbs;
 	const int* seg;          // grouped products: batch z owns rows [seg[z], seg[z+1]) of X and Y (xbs = ybs = 0), N bounds one group; null: none
 	int x_rows;              // grouped products: rows of X and Y over all groups
+	int split;               // > 0: output columns m >= split leave as relu(acc)^2 in the activation type to Y2[n][m - split] (row stride ldy2), whatever epi says
+	void* Y2;
+	long ldy2;
 };
 // rows of batch z: first row and count
 struct GemmRows {
@@ -1090,6 +1093,11 @@ __device__ __forceinline__ void gemm_store(const GemmArgs& a, int z, const GemmR
 	if (n >= gr.count || m >= a.M) return;
 	const size_t o = (size_t)z * a.ybs + (size_t)(gr.base + n) * a.ldy + m;
 	if (a.bias) acc += ldf(a.bias + (size_t)z * a.M + m);
+	if (a.split > 0 && m >= a.split) {
+		const float r = fmaxf(acc, 0.f);
+		((AT*)a.Y2)[(size_t)(gr.base + n) * a.ldy2 + (m - a.split)] = to_act<AT>(r * r);
+		return;
+	}
 	if (a.epi == EPI_F32) ((float*)a.Y)[o] = acc;
 	else if (a.epi == EPI_ACT) {
 		if (a.gate) acc *= sigmoidf_(a.gate[(size_t)z * a.gbs + (size_t)(gr.base + n) * a.ldgate + m]);

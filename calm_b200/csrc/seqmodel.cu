@@ -65,6 +65,8 @@ struct Seq {
 
 	// workspace for cap_tokens tokens
 	float *x = nullptr, *x0 = nullptr, *proj = nullptr, *f[6] = {};
+	void* ah = nullptr;                               // parallel blocks: a dense unit's hidden activations, written by the mixer's input product
+	size_t w_ah = 0;
 	float* mo = nullptr;                              // parallel blocks: the mixer's output until the feed-forward's is added with it
 	// routed experts: choices and weights per token, groups, and the grouped activations of max_top choices per token
 	int max_top = 0, max_experts = 0;
@@ -150,6 +152,11 @@ size_t in_rows(const SeqLayer& L) {
 	default: return (size_t)L.heads * L.dim + (size_t)L.kv_heads * L.dim + (size_t)L.kv_heads * L.vdim;
 	}
 }
+// row stride of the input projection's fp32 output: the mixer's rows, and a router's that ride along (rounded to whole float4s)
+int proj_stride(const SeqLayer& L) {
+	if (L.in_tail <= 0) return (int)in_rows(L);
+	return (int)((in_rows(L) + (L.ff_kind == SEQ_FF_MOE ? L.in_tail : 0) + 3) & ~(size_t)3);
+}
 int conv_channels(const SeqLayer& L) {
 	if (L.type == SEQ_DELTA) return 2 * L.kv_heads * L.dim + L.heads * L.vdim;
 	if (L.type == SEQ_WINDOW) return L.heads * L.dim + L.kv_heads * L.dim + L.kv_heads * L.vdim;
@@ -222,6 +229,8 @@ void validate(const Seq& s) {
 		} else CALM_FATAL("seq: layer %d: unknown mixer %d", i, L.type);
 		if (L.ff > 0) {
 			if (L.ff_kind < SEQ_FF_CLAMPED || L.ff_kind > SEQ_FF_MOE) CALM_FATAL("seq: layer %d: unknown feed-forward kind %d", i, L.ff_kind);
+			if (L.in_tail != 0 && (m.block != SEQ_BLOCK_PARALLEL || L.in_tail != (L.ff_kind == SEQ_FF_MOE ? L.experts : L.ff_kind == SEQ_FF_RELU2 ? L.ff : -1)))
+				CALM_FATAL("seq: layer %d: in_tail must be the router's or the up projection's row count, in a parallel block", i);
 			if (L.ff_kind == SEQ_FF_MOE) {
 				if (L.experts < 1 || L.top < 1 || L.top > L.experts) CALM_FATAL("seq: layer %d: 1 <= top <= experts", i);
 				if (m.block != SEQ_BLOCK_PARALLEL) CALM_FATAL("seq: layer %d: routed experts are served in parallel blocks only", i);
@@ -264,6 +273,7 @@ void reserve_tokens(Seq& s, int N, int B, int W) {
 		cudaFree(s.x), cudaFree(s.x0), cudaFree(s.proj), cudaFree(s.hA), cudaFree(s.a1), cudaFree(s.a2), cudaFree(s.a3), cudaFree(s.mo);
 		for (float*& p : s.f) cudaFree(p);
 		if (s.m.block == SEQ_BLOCK_PARALLEL) s.mo = (float*)dalloc(cn * s.m.width * sizeof(float));
+		if (s.w_ah) cudaFree(s.ah), s.ah = dalloc(cn * s.w_ah * act_size(s));
 		if (s.max_top > 0) {
 			cudaFree(s.moe_sel), cudaFree(s.moe_wt), cudaFree(s.moe_y), cudaFree(s.moe_d), cudaFree(s.moe_x), cudaFree(s.moe_a);
 			const size_t pairs = cn * s.max_top;
@@ -303,13 +313,16 @@ struct GemmExtra {
 	const int* seg = nullptr;    // grouped product: rows of batch z
 	int x_rows = 0;              // grouped product: rows of X / Y over all groups
 	float epi_f = 0.f;           // EPI_DECAY: exponent
+	int split = 0;               // columns from here on leave as relu(.)^2 in the activation type to Y2
+	void* Y2 = nullptr;
+	long ldy2 = 0;
 };
 void gemm(Seq& s, const void* X, long ldx, long xbs, const void* W, long ldw, long wbs, void* Y, long ldy, long ybs, int N, int M, int K, int batch, int epi,
           const SeqNorm* nrm = nullptr, int kind_as = -1, bool w_immutable = true, const GemmExtra* ex = nullptr) {
 	GemmArgs a;
 	const GemmExtra none;
 	if (!ex) ex = &none;
-	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f;
+	a.bias = (const bf16*)ex->bias, a.res = ex->res, a.gate = ex->gate, a.ldgate = ex->ldgate, a.gbs = ex->gbs, a.seg = ex->seg, a.x_rows = ex->x_rows, a.epi_f = ex->epi_f, a.split = ex->split, a.Y2 = ex->Y2, a.ldy2 = ex->ldy2;
 	a.w_immutable = w_immutable;
 	a.X = X, a.ldx = ldx, a.xbs = xbs, a.W = (const bf16*)W, a.ldw = ldw, a.wbs = wbs, a.Y = Y, a.ldy = ldy, a.ybs = ybs;
 	a.N = N, a.M = M, a.K = K, a.epi = epi;
@@ -462,7 +475,7 @@ void attention(Seq& s, int kind, AttArgs a, void* out, const SeqBatch& sb, doubl
 
 void conv(Seq& s, const SeqLayer& L, RunState& r, ConvArgs& ca, const SeqBatch& sb) {
 	const int units = ca.seg[0].heads + ca.seg[1].heads + ca.seg[2].heads;
-	ca.proj = s.proj, ca.ldp = (int)in_rows(L), ca.w = (const bf16*)L.conv, ca.taps = L.taps, ca.channels = conv_channels(L), ca.state = r.conv, ca.eps = s.m.eps;
+	ca.proj = s.proj, ca.ldp = proj_stride(L), ca.w = (const bf16*)L.conv, ca.taps = L.taps, ca.channels = conv_channels(L), ca.state = r.conv, ca.eps = s.m.eps;
 	const double bytes = (double)sb.N * ca.channels * 8;
 	run_kernel(s, KD_CONV, bytes, 0, [&] { launch_k(s, k_seq_conv_heads, dim3(sb.N, cdiv(units, 4)), 128, 0, ca, sb); });
 	if (L.taps > 1)
@@ -487,12 +500,17 @@ void out_product(Seq& s, const AT* X, const void* Wt, int N, int K, const OutEpi
 
 template <typename AT>
 void mixer_typed(Seq& s, const SeqLayer& L, RunState& r, const SeqBatch& sb, double kv_rows, int longest, const OutEpi& oe) {
-	const int N = sb.N, W = s.m.width, P = (int)in_rows(L);
+	const int N = sb.N, W = s.m.width, P = proj_stride(L);
 	AT *hA = (AT*)s.hA, *a1 = (AT*)s.a1, *a2 = (AT*)s.a2;
 	{
+		// one product for everything that reads the normed input: the mixer's rows, and in parallel blocks the router's rows (fp32, behind
+		// the mixer's) or the dense unit's up rows (leaving as relu^2 in the activation type)
 		GemmExtra gx;
 		gx.bias = L.b_in;
-		gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, P, W, 1, EPI_F32, nullptr, -1, true, &gx);
+		int M = (int)in_rows(L);
+		if (L.in_tail > 0 && L.ff_kind == SEQ_FF_MOE) M += L.in_tail;
+		if (L.in_tail > 0 && L.ff_kind == SEQ_FF_RELU2) gx.split = M, gx.Y2 = s.ah, gx.ldy2 = L.ff, M += L.in_tail;
+		gemm(s, hA, W, 0, L.w_in, W, 0, s.proj, P, 0, N, M, W, 1, EPI_F32, nullptr, -1, true, &gx);
 	}
 	if (L.type == SEQ_LATENT) {
 		const int H = L.heads, D = L.dim, Dv = L.vdim, Rq = L.q_rank, Rk = L.kv_rank;
@@ -608,15 +626,24 @@ void feed_forward(Seq& s, const SeqLayer& L, const SeqBatch& sb, const OutEpi& o
 		           [&] { launch_k(s, k_seq_ff_act<AT>, cdiv((long)N * L.ff, 256), 256, 0, a2, s.proj, L.ff, N, L.limit, 0); });
 		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
 	} else if (L.ff_kind == SEQ_FF_RELU2) {
+		if (L.in_tail > 0) { // the up rows rode in the mixer's input product
+			out_product<AT>(s, (const AT*)s.ah, L.w_down, N, L.ff, oe);
+			return;
+		}
 		gemm(s, hA, W, 0, L.w_gate_up, W, 0, a2, L.ff, 0, N, L.ff, W, 1, EPI_ACT_RELU2); // relu(up)^2 leaves the product's epilogue in the activation type
 		out_product<AT>(s, a2, L.w_down, N, L.ff, oe);
 	} else {
 		// routed experts: logits -> choices and weights -> pairs grouped by expert -> two grouped products around the unit -> weighted sum
 		const int E = L.experts, top = L.top, pairs = N * top, ff = L.ff;
-		GemmExtra rx;
-		rx.bias = L.b_router;
-		gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, E, 0, N, E, W, 1, EPI_F32, nullptr, -1, true, &rx);
-		run_kernel(s, KD_ROUTE, (double)N * E * 4, 0, [&] { launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, s.proj, E, top, N, s.moe_sel, s.moe_wt); });
+		const float* logits = s.proj;
+		int ldl = E;
+		if (L.in_tail > 0) logits = s.proj + in_rows(L), ldl = proj_stride(L); // the router's rows rode in the mixer's input product
+		else {
+			GemmExtra rx;
+			rx.bias = L.b_router;
+			gemm(s, hA, W, 0, L.w_router, W, 0, s.proj, E, 0, N, E, W, 1, EPI_F32, nullptr, -1, true, &rx);
+		}
+		run_kernel(s, KD_ROUTE, (double)N * E * 4, 0, [&] { launch_k(s, k_seq_moe_route, cdiv(N, 4), 128, 0, logits, ldl, E, top, N, s.moe_sel, s.moe_wt); });
 		run_kernel(s, KD_ROUTE, (double)pairs * 4 * E, 0, [&] { launch_k(s, k_seq_moe_group, E, 256, 0, s.moe_sel, pairs, E, s.moe_seg, s.moe_perm, s.moe_inv); });
 		run_kernel(s, KD_ELEMENT, (double)pairs * W * 2 * sizeof(AT), 0,
 		           [&] { launch_k(s, k_seq_moe_gather<AT>, cdiv((long)pairs * W, 256), 256, 0, (AT*)s.moe_x, hA, s.moe_perm, top, pairs, W); });
@@ -826,7 +853,8 @@ extern "C" void* calm_b200_seq_prepare(const struct SeqModel* model) {
 		}
 		if (L.type == SEQ_GQA) s.w_f = std::max(s.w_f, (size_t)L.heads * L.dim), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.heads * L.dim}); // a3 holds the queries
 		if (L.type == SEQ_GLA) s.w_f = std::max({s.w_f, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim}), s.w_a = std::max({s.w_a, (size_t)L.heads * L.vdim, (size_t)L.a_rank});
-		s.w_proj = std::max({s.w_proj, in_rows(L), (size_t)2 * L.ff});
+		s.w_proj = std::max({s.w_proj, (size_t)proj_stride(L), (size_t)2 * L.ff});
+		if (L.ff > 0 && L.ff_kind == SEQ_FF_RELU2 && L.in_tail > 0) s.w_ah = std::max(s.w_ah, (size_t)L.ff);
 		size_t wf = 0, wa = (size_t)L.ff;
 		if (L.type == SEQ_LATENT) wf = (size_t)L.heads * L.kv_rank, wa = std::max({wa, (size_t)L.heads * L.kv_rank, (size_t)L.heads * L.dim, (size_t)L.heads * L.vdim, (size_t)L.q_rank});
 		if (L.type == SEQ_DELTA) wf = std::max((size_t)L.heads * L.dim, (size_t)L.heads * L.vdim), wa = std::max({wa, (size_t)L.heads * L.vdim, (size_t)L.a_rank + L.g_rank});
@@ -846,7 +874,7 @@ extern "C" void calm_b200_seq_release(void* handle) {
 	cudaFree(s->part), cudaFree(s->a3), cudaFree(s->att_kb), cudaFree(s->att_vt), cudaFree(s->att_s), cudaFree(s->att_p), cudaFree(s->x), cudaFree(s->x0), cudaFree(s->proj), cudaFree(s->hA), cudaFree(s->a1), cudaFree(s->a2), cudaFree(s->trace_buf);
 	for (float* p : s->f) cudaFree(p);
 	for (double* p : s->rot_freq) cudaFree(p);
-	cudaFree(s->mo), cudaFree(s->moe_sel), cudaFree(s->moe_wt), cudaFree(s->moe_y), cudaFree(s->moe_d), cudaFree(s->moe_x), cudaFree(s->moe_a);
+	cudaFree(s->ah), cudaFree(s->mo), cudaFree(s->moe_sel), cudaFree(s->moe_wt), cudaFree(s->moe_y), cudaFree(s->moe_d), cudaFree(s->moe_x), cudaFree(s->moe_a);
 	for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
 	for (cudaEvent_t e : s->timer) cudaEventDestroy(e);
 	cudaStreamDestroy(s->stream);

@@ -30,7 +30,7 @@ class SeqLayer(C.Structure):
                                           "out_norm", "sink", "w_gate_up", "w_down", "b_in", "q_norm", "k_norm", "b_a2")] + \
                [(n, C.c_int) for n in ("keep_first", "rot_dims")] + \
                [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_original", "rot_fast", "rot_slow", "tau")] + \
-               [(n, C.c_int) for n in ("ff_kind", "experts", "top")] + [(n, C.c_void_p) for n in ("w_router", "b_router")]
+               [(n, C.c_int) for n in ("ff_kind", "experts", "top")] + [(n, C.c_void_p) for n in ("w_router", "b_router")] + [("in_tail", C.c_int)]
 
 
 class SeqModel(C.Structure):

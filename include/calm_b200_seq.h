@@ -26,7 +26,7 @@
  * Blocks (SeqModel.block): serial -- norm, mixer, norm, residual add, then the same around the feed-forward; parallel -- one
  * norm whose output both the mixer and the feed-forward read, x <- x + (mixer + feed-forward).
  * Feed-forward (SeqLayer.ff_kind): clamped gated unit, down(relu(up)^2), or a routed mixture of SiLU-gated experts (the `top`
- * largest router logits, softmax over those only).
+ * highest router scores, mixed by a softmax restricted to those scores).
  * A span of layers can be run several times in a row with the same weights (loop_*), each pass with its own state.
  */
 #ifndef CALM_B200_SEQ_H
@@ -103,6 +103,10 @@ struct SeqLayer {
 	int experts, top;      /* SEQ_FF_MOE */
 	const void* w_router;  /* (experts, width) */
 	const void* b_router;  /* bf16 [experts] or NULL */
+	/* parallel blocks: the feed-forward reads the same normed input as the mixer, so its first rows can ride in the mixer's input
+	 * product.  in_tail rows appended to w_in (and b_in): SEQ_FF_MOE: the router's `experts` rows (w_router / b_router unused);
+	 * SEQ_FF_RELU2: the `ff` rows of the up projection (w_gate_up unused); 0: the feed-forward runs its own first product */
+	int in_tail;
 };
 
 struct SeqModel {
@@ -118,7 +122,7 @@ struct SeqModel {
 	struct SeqNorm final_norm;
 	const struct SeqLayer* layers;
 	int norm_kind;      /* enum SeqNormKind */
-	float norm_offset;  /* SEQ_NORM_RMS: added to the stored weight (1 for weights stored around zero) */
+	float norm_offset;  /* SEQ_NORM_RMS: added to the stored weight (1 when the checkpoint keeps weights as offsets from one) */
 	int block;          /* enum SeqBlock */
 	float embed_scale;  /* factor on the embedding rows (0 is read as 1) */
 };

@@ -12,7 +12,7 @@ import numpy as np
 
 
 def rms_norm(x: np.ndarray, w: np.ndarray, eps: float, around_zero: bool) -> np.ndarray:
-    """x / sqrt(mean(x^2) + eps) times w, or times (1 + w) when the weight is stored around zero."""
+    """x / sqrt(mean(x^2) + eps) times w, or times (1 + w) when the checkpoint keeps the weight as its offset from one."""
     r = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
     return r * (1.0 + w) if around_zero else r * w
 
@@ -112,7 +112,7 @@ def dense_ff(h: np.ndarray, W: Dict[str, np.ndarray]) -> np.ndarray:
 
 
 def route(h: np.ndarray, W: Dict[str, np.ndarray], top: int):
-    """Per token: the `top` experts with the largest router logits and the softmax over those logits only."""
+    """Per token: which `top` experts score highest at the router, and their mixing weights (a softmax restricted to those scores)."""
     z = h @ W["router"].T + W["router.b"]
     idx = np.argsort(-z, axis=-1, kind="stable")[:, :top]
     zs = np.take_along_axis(z, idx, -1)

@@ -268,7 +268,7 @@ def test_tensor_core_products_match_the_warp_level_ones(monkeypatch):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_one_expert_takes_every_token(dtype):
     """A router bias that puts one expert among every token's choices: its group spans several tiles of the grouped products,
-    other groups are short or empty, and the weights stay the softmax over the chosen logits only."""
+    other groups are short or empty, and the mixing weights stay a softmax restricted to the scores of the experts taken."""
     cfg = config([gla(mlp=moe(experts=7, top=2, ff=16)), attn(mlp=moe(experts=4, top=1, ff=16))])
     t, toks = weights(cfg, 18, favour=(2, 30.0)), tokens(cfg, 200)
     ref = plain.forward(cfg, as_f64(t), toks)
@@ -324,7 +324,7 @@ def test_slots_and_pages_are_used_again():
     p = as_f64(t)
     with bovinex.from_tensors(cfg, t, "float32", max_tokens=48, max_seqs=2, page=4) as m:
         free0 = m.free_pages()
-        for rnd in range(4):  # every round fills the pool almost completely, with other lengths than the round before
+        for rnd in range(4):  # every pass fills the pool almost completely, with other lengths than the pass before
             a, b = tokens(cfg, 20 + rnd, seed=rnd), tokens(cfg, 23 - rnd, seed=9 + rnd)
             sa, sb = m.open(), m.open()
             out = m.step([sa, sb], [a, b], list(range(len(a) + len(b))))

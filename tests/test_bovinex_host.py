@@ -31,14 +31,18 @@ def test_plan_stacks_inputs_in_kernel_order():
     t = bovinex.random_tensors(cfg, 1)
     head, layers, up = bovinex.plan(cfg, t)
     assert head["norm_kind"] == seqlib.NORM_RMS and head["norm_offset"] == 1.0 and head["block"] == seqlib.BLOCK_PARALLEL and head["embed_scale"] == 4.0
-    assert torch.equal(up["l0.mix.in"], torch.cat([t["l0.mix." + n] for n in ("q", "k", "v", "g", "a1")]))
-    assert torch.equal(up["l1.mix.in"], torch.cat([t["l1.mix." + n] for n in ("q", "k", "v", "g")]))
-    assert torch.equal(up["l1.mix.in.b"], torch.cat([t["l1.mix.q.b"], t["l1.mix.k.b"], t["l1.mix.v.b"], torch.zeros(16, dtype=torch.bfloat16)]))
+    # what reads the normed input is one matrix per layer: the mixer's rows, then the router's or the dense unit's up rows
+    assert torch.equal(up["l0.mix.in"], torch.cat([t["l0.mix." + n] for n in ("q", "k", "v", "g", "a1")] + [t["l0.mlp.router"]]))
+    assert torch.equal(up["l0.mix.in.b"], torch.cat([torch.zeros(2 * 8 + 2 * 16 + 3, dtype=torch.bfloat16), t["l0.mlp.router.b"]]))
+    assert torch.equal(up["l1.mix.in"], torch.cat([t["l1.mix." + n] for n in ("q", "k", "v", "g")] + [t["l1.mlp.up"]]))
+    assert torch.equal(up["l1.mix.in.b"], torch.cat([t["l1.mix.q.b"], t["l1.mix.k.b"], t["l1.mix.v.b"], torch.zeros(16 + 12, dtype=torch.bfloat16)]))
+    assert torch.equal(up["l2.mix.in"], torch.cat([t["l2.mix." + n] for n in ("q", "k", "v", "g")])) and up["l2.mix.in.b"].shape == (8 + 8 + 8 + 8,)
     assert up["l0.mlp.gate_up"].shape == (3 * 12, 16) and torch.equal(up["l0.mlp.gate_up"][12:18], t["l0.mlp.e1.gate"]) and torch.equal(up["l0.mlp.gate_up"][18:24], t["l0.mlp.e1.up"])
     assert torch.equal(up["l0.mlp.downs"][32:48], t["l0.mlp.e2.down"])
     g, a, plainattn = layers
-    assert g["type"] == seqlib.SEQ_GLA and g["a_rank"] == 3 and g["ff_kind"] == seqlib.FF_MOE and (g["experts"], g["top"], g["ff"]) == (3, 2, 6) and g["tau"] == 8.0
+    assert g["type"] == seqlib.SEQ_GLA and g["a_rank"] == 3 and g["ff_kind"] == seqlib.FF_MOE and (g["experts"], g["top"], g["ff"], g["in_tail"]) == (3, 2, 6, 3) and g["tau"] == 8.0
     assert a["type"] == seqlib.SEQ_GQA and (a["window"], a["keep_first"], a["rot_dims"], a["rot_factor"], a["rot_original"]) == (5, 2, 4, 2.0, 32.0) and a["ff_kind"] == seqlib.FF_RELU2
+    assert a["in_tail"] == a["ff"] == 12 and "w_gate_up" not in a and "w_router" not in g and "l1.mlp.up" not in up and "l0.mlp.router" not in up
     assert (plainattn["window"], plainattn["keep_first"], plainattn["rot_dims"], plainattn["rot_factor"]) == (0, 0, 0, 0.0) and "ff" not in plainattn
     bad = dict(t)
     bad["l1.mix.k.norm"] = bad["l1.mix.k.norm"][:-1]
